@@ -61,11 +61,13 @@ class LayerSpec:
     mixer: PartSpec
     feed_forward: Optional[PartSpec]
     norms_items: Tuple[Tuple[str, PartSpec], ...]
+    # a term that the layer adds behind its sublayers from the step's tokens (a block kind that takes one), or None
+    token_input: Optional[PartSpec] = None
 
     @classmethod
     def make(cls, block: str, mixer: PartSpec, feed_forward: Optional[PartSpec],
-             norms: Mapping[str, PartSpec]) -> "LayerSpec":
-        return cls(block, mixer, feed_forward, tuple(sorted(norms.items())))
+             norms: Mapping[str, PartSpec], token_input: Optional[PartSpec] = None) -> "LayerSpec":
+        return cls(block, mixer, feed_forward, tuple(sorted(norms.items())), token_input)
 
     @property
     def norms(self) -> Dict[str, PartSpec]:

@@ -33,13 +33,35 @@ namespace {
 constexpr int kWarps = 4;
 enum MaskKind : int { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_BLOCKS = 2 };
 
+// Where a page keeps what.  keys_per_value >= 1: [kv_heads][page][dim] keys, then [kv_heads / keys_per_value][page][vdim]
+// values, key head g reading value head g / keys_per_value (1: the usual layout; 2: two score maps over one set of
+// values).  keys_per_value == 0: the page holds keys only, and a key's first vdim numbers are its value (attention in a
+// latent space).
+struct PageLayout {
+    int64_t page_elems, value_base;
+    int value_row;
+    __device__ PageLayout(int kv_heads, int kv_head, int page_size, int dim, int vdim, int keys_per_value) {
+        if (keys_per_value == 0) {
+            page_elems = (int64_t)kv_heads * page_size * dim;
+            value_base = (int64_t)kv_head * page_size * dim;
+            value_row = dim;
+        } else {
+            const int value_heads = kv_heads / keys_per_value;
+            page_elems = (int64_t)page_size * ((int64_t)kv_heads * dim + (int64_t)value_heads * vdim);
+            value_base = (int64_t)kv_heads * page_size * dim + (int64_t)(kv_head / keys_per_value) * page_size * vdim;
+            value_row = vdim;
+        }
+    }
+};
+
 template <typename T, int NCV, bool VEC>
 __global__ void __launch_bounds__(kWarps * 32)
 attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ gate, int64_t gate_stride,
                         T* __restrict__ out, int64_t out_stride, const T* __restrict__ cache,
                         const int* __restrict__ positions, const int* __restrict__ seq_of_row,
                         const int* __restrict__ block_table, int bt_stride, int heads, int kv_heads, int dim, int vdim,
-                        int page_size, int mask_kind, int mask_size, int sink, float scale) {
+                        int page_size, int mask_kind, int mask_size, int sink, float scale, int keys_per_value,
+                        int out_f32) {
     extern __shared__ float q_smem[];                 // kWarps * dim
     pdl_trigger();
     pdl_wait();                                       // queries, pages and the step's metadata come from kernels in front
@@ -59,9 +81,11 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
     for (int i = lane; i < dim; i += 32) qs[i] = Elem<T>::load(qrow + i);
     __syncwarp();
 
-    const int64_t page_elems = (int64_t)kv_heads * page_size * (dim + vdim);
+    const PageLayout layout(kv_heads, kv_head, page_size, dim, vdim, keys_per_value);
+    const int64_t page_elems = layout.page_elems;
+    const int vrow = layout.value_row;
     const T* kbase = cache + (int64_t)kv_head * page_size * dim;
-    const T* vbase = cache + (int64_t)kv_heads * page_size * dim + (int64_t)kv_head * page_size * vdim;
+    const T* vbase = cache + layout.value_base;
     const int* table = block_table + (int64_t)seq * bt_stride;
 
     float m = sink ? 0.0f : -1.0e30f;
@@ -78,7 +102,7 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
         if (valid) {
             const int64_t page = table[key / page_size];
             const int in_page = key % page_size;
-            v_offset = page * page_elems + (int64_t)in_page * vdim;
+            v_offset = page * page_elems + (int64_t)in_page * vrow;
             const T* kp = kbase + page * page_elems + (int64_t)in_page * dim;
             float dot = 0.0f;
             if (VEC) {
@@ -114,7 +138,7 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
         m = m_new;
     }
     const float denom = fmaxf(l, 1.0e-30f);
-    T* orow = out + (int64_t)row * out_stride + (int64_t)head * vdim;
+    const int64_t oat = (int64_t)row * out_stride + (int64_t)head * vdim;
     const T* grow = gate == nullptr ? nullptr : gate + (int64_t)row * gate_stride + (int64_t)head * vdim;
 #pragma unroll
     for (int c = 0; c < NCV; ++c) {
@@ -122,7 +146,8 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
         if (col < vdim) {
             float value = acc[c] / denom;
             if (grow != nullptr) value *= 1.0f / (1.0f + expf(-Elem<T>::load(grow + col)));
-            Elem<T>::store(orow + col, value);
+            if (out_f32) reinterpret_cast<float*>(out)[oat + col] = value;
+            else Elem<T>::store(out + oat + col, value);
         }
     }
 }
@@ -146,7 +171,7 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
                                 const T* __restrict__ cache, const int* __restrict__ positions,
                                 const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride,
                                 int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
-                                int mask_size, int sink, float scale, int lv) {
+                                int mask_size, int sink, float scale, int lv, int keys_per_value, int out_f32) {
     constexpr int N = Packet<T>::N;
     constexpr bool SPLIT = SPLITW > 0;
     constexpr int WARPS = SPLIT ? SPLITW : kRowsPerBlock;
@@ -172,9 +197,11 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
     for (int i = lane * N; i < HPW * dim; i += 32 * N) Packet<T>::load(qrow + i, qs + i);
     __syncwarp();
 
-    const int64_t page_elems = (int64_t)kv_heads * page_size * (dim + vdim);
+    const PageLayout layout(kv_heads, kv_head, page_size, dim, vdim, keys_per_value);
+    const int64_t page_elems = layout.page_elems;
+    const int vrow = layout.value_row;
     const T* kbase = cache + (int64_t)kv_head * page_size * dim;
-    const T* vbase = cache + (int64_t)kv_heads * page_size * dim + (int64_t)kv_head * page_size * vdim;
+    const T* vbase = cache + layout.value_base;
     const int* table = block_table + (int64_t)seq * bt_stride;
     const int vg = lane / lv, vs = lane % lv;         // value phase: group vg owns keys vg, vg + 32 / lv, ...
     const int value_step = 32 / lv;
@@ -199,7 +226,7 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
         const int in_page = k % page_size;
         const T* kp = kbase + base + (int64_t)in_page * dim;
         __syncwarp();                                 // the value phase of the block before has read voffs and ps
-        voffs[lane] = base + (int64_t)in_page * vdim;
+        voffs[lane] = base + (int64_t)in_page * vrow;
         // scores: a lane a key, the key's packets against the HPW queries in shared memory
         float dot[HPW];
 #pragma unroll
@@ -322,7 +349,7 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
 #pragma unroll
     for (int h = 0; h < HPW; ++h) {
         const float inv = 1.0f / fmaxf(l[h], 1.0e-30f);
-        T* orow = out + (int64_t)row * out_stride + (int64_t)(head0 + h) * vdim;
+        const int64_t oat = (int64_t)row * out_stride + (int64_t)(head0 + h) * vdim;
         const T* grow = gate == nullptr ? nullptr : gate + (int64_t)row * gate_stride + (int64_t)(head0 + h) * vdim;
 #pragma unroll
         for (int pk = 0; pk < NP; ++pk) {
@@ -337,7 +364,12 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
 #pragma unroll
                     for (int e = 0; e < N; ++e) value[e] *= __fdividef(1.0f, 1.0f + __expf(-gv[e]));
                 }
-                Packet<T>::store(orow + col, value);
+                if (out_f32) {
+#pragma unroll
+                    for (int e = 0; e < N; e += 4) Packet<float>::store(reinterpret_cast<float*>(out) + oat + col + e, value + e);
+                } else {
+                    Packet<T>::store(out + oat + col, value);
+                }
             }
         }
     }
@@ -349,7 +381,7 @@ template <typename T, int HPW, int NP, int SPLITW>
 int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out,
                       int64_t out_stride, const void* cache, const int* positions, const int* seq_of_row,
                       const int* block_table, int bt_stride, int rows, int heads, int kv_heads, int dim, int vdim,
-                      int page_size, int mask_kind, int mask_size, int sink, float scale, cudaStream_t stream) {
+                      int page_size, int mask_kind, int mask_size, int sink, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
     constexpr int N = Packet<T>::N;
     int lv = 1;
     while (lv < 32 && lv * NP < vdim / N) lv <<= 1;
@@ -366,7 +398,7 @@ int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t
     cudaError_t launched = tb_launch_pdl(kernel, grid, dim3(WARPS * 32), smem, stream, (const T*)q, q_stride,
                                          (const T*)gate, gate_stride, (T*)out, out_stride, (const T*)cache, positions,
                                          seq_of_row, block_table, bt_stride, rows, heads, kv_heads, dim, vdim,
-                                         page_size, mask_kind, mask_size, sink, scale, lv);
+                                         page_size, mask_kind, mask_size, sink, scale, lv, keys_per_value, out_f32);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
@@ -374,7 +406,7 @@ template <typename T>
 int launch_packets(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
                    const void* cache, const int* positions, const int* seq_of_row, const int* block_table,
                    int bt_stride, int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
-                   int mask_size, int sink, float scale, cudaStream_t stream) {
+                   int mask_size, int sink, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
     const int per = heads / kv_heads;
     const bool two = vdim / Packet<T>::N > 32;        // more value packets than lanes: two a lane
     // (which form runs depends on the step's row count and the mask alone)
@@ -382,7 +414,7 @@ int launch_packets(const void* q, int64_t q_stride, const void* gate, int64_t ga
 #define TB_PACKETS_AS(HPW, NP, SPLITW)                                                                               \
     launch_packets_as<T, HPW, NP, SPLITW>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions,         \
                                           seq_of_row, block_table, bt_stride, rows, heads, kv_heads, dim, vdim,      \
-                                          page_size, mask_kind, mask_size, sink, scale, stream)
+                                          page_size, mask_kind, mask_size, sink, scale, keys_per_value, out_f32, stream)
 #define TB_PACKETS(HPW, NP)                                                                                          \
     return rows > kSplitMaxRows ? TB_PACKETS_AS(HPW, NP, 0)                                                          \
                                 : (long_span ? TB_PACKETS_AS(HPW, NP, kSplitWarpsLong) : TB_PACKETS_AS(HPW, NP, kSplitWarps))
@@ -399,13 +431,14 @@ template <typename T, bool VEC>
 int launch_vec(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
                const void* cache, const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
                int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind, int mask_size,
-               int sink, float scale, cudaStream_t stream) {
+               int sink, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
     const dim3 grid(rows, (heads + kWarps - 1) / kWarps);
     const size_t smem = (size_t)kWarps * dim * sizeof(float);
 #define TB_LAUNCH(NCV)                                                                                              \
     tb_launch_pdl(attention_masked_kernel<T, NCV, VEC>, grid, dim3(kWarps * 32), smem, stream, (const T*)q, q_stride,   \
                   (const T*)gate, gate_stride, (T*)out, out_stride, (const T*)cache, positions, seq_of_row,         \
-                  block_table, bt_stride, heads, kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink, scale)
+                  block_table, bt_stride, heads, kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink, scale, keys_per_value, \
+                  out_f32)
     if (vdim <= 32) TB_LAUNCH(1);
     else if (vdim <= 64) TB_LAUNCH(2);
     else if (vdim <= 96) TB_LAUNCH(3);
@@ -421,7 +454,7 @@ template <typename T>
 int launch(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
            const void* cache, const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
            int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind, int mask_size, int sink,
-           float scale, cudaStream_t stream) {
+           float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
     // 16-byte key loads need every key row to start on a 16-byte boundary
     const bool vec = dim % Packet<T>::N == 0 && vdim % Packet<T>::N == 0 && (uintptr_t)cache % 16 == 0;
     const uintptr_t bits = (uintptr_t)q | (uintptr_t)gate | (uintptr_t)out;
@@ -430,38 +463,41 @@ int launch(const void* q, int64_t q_stride, const void* gate, int64_t gate_strid
     if (vec && rows_in_packets && vdim <= 64 * Packet<T>::N && dim <= 64 * Packet<T>::N)
         return launch_packets<T>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                  block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
-                                 mask_size, sink, scale, stream);
+                                 mask_size, sink, scale, keys_per_value, out_f32, stream);
     if (vec)
         return launch_vec<T, true>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                    block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
-                                   mask_size, sink, scale, stream);
+                                   mask_size, sink, scale, keys_per_value, out_f32, stream);
     return launch_vec<T, false>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                 block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
-                                mask_size, sink, scale, stream);
+                                mask_size, sink, scale, keys_per_value, out_f32, stream);
 }
 
 }  // namespace
 
 // q: [rows, heads * dim] (row stride q_stride, elements); gate: null or [rows, heads * vdim] (row stride
-// gate_stride); out: [rows, heads * vdim]; cache: this layer's pages.  mask_kind: 0 causal, 1 window, 2 blocks.
+// gate_stride); out: [rows, heads * vdim], float32 if out_f32 (out_stride then counts floats) and else the dtype of q;
+// cache: this layer's pages, laid out as keys_per_value says (PageLayout).  mask_kind: 0 causal, 1 window, 2 blocks.
 TB_EXPORT int tb_attention_masked(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out,
                                   int64_t out_stride, const void* cache, const int* positions, const int* seq_of_row,
                                   const int* block_table, int bt_stride, int rows, int heads, int kv_heads, int dim,
                                   int vdim, int page_size, int mask_kind, int mask_size, int sink, float scale,
-                                  int dtype, cudaStream_t stream) {
+                                  int keys_per_value, int out_f32, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
     if (dim < 1 || dim > 1024 || vdim < 1 || vdim > 512) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || page_size < 1) return TB_ERR_BAD_SIZE;
     if (mask_kind < MASK_CAUSAL || mask_kind > MASK_BLOCKS) return TB_ERR_BAD_SIZE;
     if (mask_kind != MASK_CAUSAL && mask_size < 1) return TB_ERR_BAD_SIZE;
     if ((heads + kWarps - 1) / kWarps > 65535) return TB_ERR_BAD_SIZE;
+    if (keys_per_value < 0 || (keys_per_value > 0 && kv_heads % keys_per_value != 0)) return TB_ERR_BAD_SIZE;
+    if (keys_per_value == 0 && vdim > dim) return TB_ERR_BAD_SIZE;
     if (dtype == TB_F32)
         return launch<float>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row, block_table,
                              bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink, scale,
-                             stream);
+                             keys_per_value, out_f32, stream);
     if (dtype == TB_BF16)
         return launch<__nv_bfloat16>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                      block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
-                                     mask_size, sink, scale, stream);
+                                     mask_size, sink, scale, keys_per_value, out_f32, stream);
     return TB_ERR_BAD_DTYPE;
 }

@@ -59,6 +59,10 @@ SOURCES: Dict[str, List[str]] = {
     "rope_norm_cache": [],
     "experts": [],
     "attention_prompt_mma": [],
+    "sandwich_norm": [],
+    "lightning": [],
+    "differential": [],
+    "latent_rope_cache": [],
 }
 
 

@@ -10,6 +10,8 @@
 //   tb_scale_rows         y[t, j] *= s                         (32-bit y)
 //   tb_add_rows           a[t, j] += b[t, j]                   (32-bit)
 //   tb_embedding_scaled   out[t, :] = float(table[token[t], :]) * s   (32-bit out; the table 32-bit or bfloat16)
+//   tb_token_gate         out[t, j] = act(z[t, j]) * table[token[t], offset + j]     (32-bit z; a slice of a second
+//                         embedding table gated by a projection of the stream)
 #include "common.cuh"
 
 namespace {
@@ -114,6 +116,20 @@ __global__ void embedding_scaled_kernel(const int* __restrict__ tokens, const T*
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Elem<T>::load(src + i) * s;
 }
 
+template <typename T, int ACT>
+__global__ void token_gate_kernel(const float* __restrict__ z, const int* __restrict__ tokens,
+                                  const T* __restrict__ table, int64_t table_stride, int offset, T* __restrict__ out,
+                                  int width, int vocab) {
+    pdl_trigger();
+    pdl_wait();
+    int from = tokens[blockIdx.x];
+    if (from < 0 || from >= vocab) from = 0;      // the host validates; never read out of bounds
+    const T* e = table + (int64_t)from * table_stride + offset;
+    for (int j = threadIdx.x; j < width; j += blockDim.x)
+        Elem<T>::store(out + (int64_t)blockIdx.x * width + j,
+                       activate<ACT>(z[(int64_t)blockIdx.x * width + j]) * Elem<T>::load(e + j));
+}
+
 inline dim3 row_grid(int rows, int width, int threads, int per_thread = 1) {
     int by = (width + threads * per_thread - 1) / (threads * per_thread);
     if (by > 64) by = 64;
@@ -216,5 +232,24 @@ TB_EXPORT int tb_embedding_scaled(const int* tokens, const void* table, int tabl
                                  (const __nv_bfloat16*)table, out, hidden, vocab, s);
     else
         return TB_ERR_BAD_DTYPE;
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+// z: float32 [rows, width]; table: [vocab, table_stride] in `dtype`, the row's slice starts at column `offset`;
+// out: [rows, width] in `dtype`.
+TB_EXPORT int tb_token_gate(const float* z, const int* tokens, const void* table, int64_t table_stride, int offset,
+                            void* out, int rows, int width, int vocab, int activation, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (width < 1 || offset < 0 || offset + width > table_stride) return TB_ERR_BAD_SIZE;
+    if (activation != ACT_SILU && activation != ACT_GELU_TANH) return TB_ERR_BAD_SIZE;
+    const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
+    cudaError_t launched;
+#define TB_RUN(T, ACT)                                                                                                \
+    launched = tb_launch_pdl(token_gate_kernel<T, ACT>, dim3(rows), dim3(threads), 0, stream, z, tokens, (const T*)table, \
+                             table_stride, offset, (T*)out, width, vocab)
+    if (dtype == TB_F32) { if (activation == ACT_SILU) TB_RUN(float, ACT_SILU); else TB_RUN(float, ACT_GELU_TANH); }
+    else if (dtype == TB_BF16) { if (activation == ACT_SILU) TB_RUN(__nv_bfloat16, ACT_SILU); else TB_RUN(__nv_bfloat16, ACT_GELU_TANH); }
+    else return TB_ERR_BAD_DTYPE;
+#undef TB_RUN
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }

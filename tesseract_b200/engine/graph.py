@@ -41,6 +41,8 @@ def graph_safe(model) -> bool:
     parts = [model.embedding, model.final_norm, model.head] + list(getattr(model, "injections", ()))
     for block in model.layers:
         parts += [block.mixer, *block.norms.values()] + ([block.feed_forward] if block.feed_forward is not None else [])
+        if getattr(block, "token_input", None) is not None:
+            parts.append(block.token_input)
     return all(getattr(part, "graph_safe", False) for part in parts)
 
 

@@ -812,15 +812,21 @@ MASK_CAUSAL, MASK_WINDOW, MASK_BLOCKS = 0, 1, 2
 def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, cache: torch.Tensor,
                      positions: torch.Tensor, seq_of_row: torch.Tensor, block_table: torch.Tensor, *, heads: int,
                      kv_heads: int, dim: int, vdim: int, page_size: int, mask_kind: int, mask_size: int, sink: bool,
-                     scale: float) -> torch.Tensor:
+                     scale: float, keys_per_value: int = 1) -> torch.Tensor:
     """Paged attention with 32-bit scores and weights: ``q`` ``[T, heads * dim]``, optional ``gate``
-    ``[T, heads * vdim]`` (the output is multiplied by its sigmoid), ``out`` ``[T, heads * vdim]``; pages hold
-    ``[kv_heads, page_size, dim]`` keys then ``[kv_heads, page_size, vdim]`` values.  ``mask_kind``: causal, window
-    or blocks of ``mask_size`` positions; ``sink``: one more entry of score 0 in the softmax's denominator."""
+    ``[T, heads * vdim]`` (the output is multiplied by its sigmoid), ``out`` ``[T, heads * vdim]`` in the dtype of ``q``
+    or in float32 (the weighted sums as they are, unrounded); pages hold ``[kv_heads, page_size, dim]`` keys then
+    ``[kv_heads / keys_per_value, page_size, vdim]`` values, key head ``g`` reading value head ``g // keys_per_value``;
+    ``keys_per_value = 0``: pages hold keys only and a key's first ``vdim`` numbers are its value.  ``mask_kind``:
+    causal, window or blocks of ``mask_size`` positions; ``sink``: one more entry of score 0 in the softmax's
+    denominator."""
     _cuda(q, gate, out, cache, positions, seq_of_row, block_table)
     rows = q.shape[0]
     _need(q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_masked q")
-    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype == q.dtype, "attention_masked out")
+    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype in (q.dtype, torch.float32),
+          "attention_masked out")
+    _need(keys_per_value >= 0 and (keys_per_value == 0 or kv_heads % keys_per_value == 0) and
+          (keys_per_value != 0 or vdim <= dim), "attention_masked keys_per_value")
     _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_masked cache")
     if gate is not None:
         _need(gate.stride(1) == 1 and gate.shape == (rows, heads * vdim) and gate.dtype == q.dtype, "attention_masked gate")
@@ -829,8 +835,9 @@ def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
                                    _ptr(out), _i64(out.stride(0)), _ptr(cache), _ptr(positions), _ptr(seq_of_row),
                                    _ptr(block_table), _i32(block_table.stride(0)), _i32(rows), _i32(heads),
                                    _i32(kv_heads), _i32(dim), _i32(vdim), _i32(page_size), _i32(mask_kind),
-                                   _i32(mask_size), _i32(1 if sink else 0), _f32(scale), _i32(_code(q.dtype)),
-                                   _stream()), "attention_masked")
+                                   _i32(mask_size), _i32(1 if sink else 0), _f32(scale), _i32(keys_per_value),
+                                   _i32(1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0),
+                                   _i32(_code(q.dtype)), _stream()), "attention_masked")
     return out
 
 
@@ -1114,3 +1121,180 @@ def expert_combine(y: torch.Tensor, weights: torch.Tensor, base: Optional[torch.
     _check(lib.tb_expert_combine(_ptr(y), _ptr(weights), _ptr(base), _ptr(out), _i32(rows), _i32(width), _i32(top),
                                  _stream()), "expert_combine")
     return out
+
+
+# ----------------------------------------------------------------------------- sublayers normed on both sides
+
+NORM_NONE, NORM_LAYER, NORM_RMS = 0, 1, 2
+
+
+def norm_add_norm(residual: torch.Tensor, update: Optional[torch.Tensor], post, following,
+                  out: Optional[torch.Tensor], copy: Optional[torch.Tensor], eps: float) -> None:
+    """``residual += post(update)`` (32-bit, in place; without ``update`` the stream stays), then ``out =
+    following(residual)`` and ``copy = residual``, both rounded once to their dtype.  ``post`` and ``following`` are
+    ``None`` or ``(kind, weight, bias)`` with kind ``NORM_LAYER`` (``(v - mean) / sqrt(var + eps) * weight + bias``) or
+    ``NORM_RMS`` (``v / sqrt(mean(v^2) + eps) * weight``, bias None); both use ``eps``."""
+    _cuda(residual, update, out, copy)
+    rows, width = residual.shape
+    _f32_rows(residual, (rows, width), "norm_add_norm: the stream is contiguous float32")
+    _f32_rows(update, (rows, width), "norm_add_norm update")
+    _need(post is None or update is not None, "norm_add_norm: a norm of the update needs an update")
+    _need((following is None) == (out is None), "norm_add_norm: the following norm needs its output")
+    dtype = None
+    for o in (out, copy):
+        if o is not None:
+            _need(tuple(o.shape) == (rows, width) and o.is_contiguous() and dtype in (None, o.dtype), "norm_add_norm out/copy")
+            dtype = o.dtype
+
+    def parts(norm):
+        if norm is None:
+            return NORM_NONE, None, None
+        kind, weight, bias = norm
+        _need(kind in (NORM_LAYER, NORM_RMS), "norm_add_norm: unknown norm kind")
+        for v in (weight, bias):
+            _need(v is None or (v.is_cuda and v.dtype == torch.float32 and v.numel() == width and v.is_contiguous()),
+                  "norm_add_norm weight/bias")
+        _need(weight is not None and (kind != NORM_LAYER or bias is not None), "norm_add_norm: a norm needs its vectors")
+        return kind, weight, bias
+
+    post_kind, post_w, post_b = parts(post)
+    next_kind, next_w, next_b = parts(following)
+    lib = load_library("sandwich_norm")
+    _check(lib.tb_norm_add_norm(_ptr(residual), _ptr(update), _i32(post_kind), _ptr(post_w), _ptr(post_b), _i32(next_kind),
+                                _ptr(next_w), _ptr(next_b), _ptr(out), _ptr(copy), _i32(rows), _i32(width), _f32(eps),
+                                _i32(_code(dtype) if dtype is not None else 0), _stream()), "norm_add_norm")
+
+
+def gated_rms_norm(v: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, eps: float) -> torch.Tensor:
+    """``out = v / sqrt(mean(v^2) + eps) * weight * sigmoid(gate)`` over rows of float32 ``v``; ``gate`` and ``out`` in
+    the run dtype."""
+    _cuda(v, weight, gate, out)
+    rows, width = v.shape
+    _f32_rows(v, (rows, width), "gated_rms_norm takes contiguous float32 rows")
+    _need(weight.dtype == torch.float32 and weight.numel() == width and weight.is_contiguous(), "gated_rms_norm weight")
+    _need(gate.stride(1) == 1 and tuple(gate.shape) == (rows, width) and out.is_contiguous()
+          and tuple(out.shape) == (rows, width) and out.dtype == gate.dtype, "gated_rms_norm gate/out")
+    lib = load_library("sandwich_norm")
+    _check(lib.tb_gated_rms_norm(_ptr(v), _ptr(weight), _ptr(gate), _i64(gate.stride(0)), _ptr(out), _i32(rows), _i32(width),
+                                 _f32(eps), _i32(_code(out.dtype)), _stream()), "gated_rms_norm")
+    return out
+
+
+def token_gate(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, offset: int, out: torch.Tensor,
+               activation: int) -> torch.Tensor:
+    """``out[t] = act(z[t]) * table[tokens[t], offset : offset + width]``: ``z`` float32 ``[T, width]``, ``table`` and
+    ``out`` in the run dtype."""
+    _cuda(z, tokens, table, out)
+    rows, width = z.shape
+    _f32_rows(z, (rows, width), "token_gate takes contiguous float32 rows")
+    _need(tokens.dtype == torch.int32 and tokens.is_contiguous() and tokens.numel() >= rows, "token_gate tokens")
+    _need(table.stride(1) == 1 and 0 <= offset and offset + width <= table.shape[1], "token_gate table")
+    _need(out.is_contiguous() and tuple(out.shape) == (rows, width) and out.dtype == table.dtype, "token_gate out")
+    lib = load_library("pointwise")
+    _check(lib.tb_token_gate(_ptr(z), _ptr(tokens), _ptr(table), _i64(table.stride(0)), _i32(offset), _ptr(out), _i32(rows),
+                             _i32(width), _i32(table.shape[0]), _i32(activation), _i32(_code(out.dtype)), _stream()),
+           "token_gate")
+    return out
+
+
+# ----------------------------------------------------------------------------- linear attention with a decay
+
+
+def lightning(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_start: torch.Tensor,
+              state_slots: torch.Tensor, *, num_seqs: int, heads: int, dim: int, vdim: int, max_new: int) -> torch.Tensor:
+    """``S_t = decay_h S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` per head with ``q, k, v = silu`` of the columns
+    ``[heads * dim | heads * dim | heads * vdim]`` of ``proj``; ``state`` float32 ``[slots, heads, dim, vdim]`` is read and
+    renewed per sequence; ``out`` float32 ``[T, heads * vdim]``."""
+    _cuda(proj, decay, state, out, row_start, state_slots)
+    rows = out.shape[0]
+    _need(proj.stride(1) == 1 and proj.shape[0] == rows and proj.shape[1] >= heads * (2 * dim + vdim), "lightning proj")
+    _f32_rows(out, (rows, heads * vdim), "lightning out is contiguous float32")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "lightning state")
+    _need(decay.dtype == torch.float32 and decay.numel() == heads and decay.is_contiguous(), "lightning decay")
+    _need(row_start.dtype == torch.int32 and state_slots.dtype == torch.int32, "lightning metadata must be int32")
+    lib = load_library("lightning")
+    _check(lib.tb_lightning(_ptr(proj), _i64(proj.stride(0)), _i32(0), _i32(heads * dim), _i32(2 * heads * dim), _ptr(decay),
+                            _ptr(state), _ptr(out), _ptr(row_start), _ptr(state_slots), _i32(num_seqs), _i32(heads),
+                            _i32(dim), _i32(vdim), _i32(max(1, max_new)), _i32(_code(proj.dtype)), _stream()), "lightning")
+    return out
+
+
+# ----------------------------------------------------------------------------- two score maps over one set of values
+
+
+def pair_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                    seq_of_row: torch.Tensor, block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], *,
+                    q_heads: int, key_heads: int, value_heads: int, dim: int, vdim: int, rot_dims: int,
+                    page_size: int) -> None:
+    """Rotation of neighbouring pairs of the first ``rot_dims`` numbers of every query and key head of ``proj``
+    (``[q_heads * dim | key_heads * dim | value_heads * vdim | ...]``); queries into ``q_out``, keys and values into the
+    pages of ``cache`` (``[key_heads, page, dim]`` keys then ``[value_heads, page, vdim]`` values)."""
+    _cuda(proj, q_out, cache, positions, seq_of_row, block_table, inv_freq)
+    rows = q_out.shape[0]
+    channels = (q_heads + key_heads) * dim + value_heads * vdim
+    _need(proj.stride(1) == 1 and proj.shape[1] >= channels and proj.shape[0] == rows, "pair_rope_cache proj")
+    _need(q_out.stride(1) == 1 and q_out.shape[1] == q_heads * dim and q_out.dtype == proj.dtype, "pair_rope_cache q_out")
+    _need(cache.dtype == proj.dtype and cache.is_contiguous(), "pair_rope_cache cache dtype")
+    if rot_dims:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2
+              and inv_freq.is_contiguous(), "pair_rope_cache inv_freq")
+    for t in (positions, seq_of_row, block_table):
+        _need(t.dtype == torch.int32, "pair_rope_cache metadata must be int32")
+    lib = load_library("differential")
+    _check(lib.tb_pair_rope_cache(_ptr(proj), _i64(proj.stride(0)), _ptr(q_out), _i64(q_out.stride(0)), _ptr(cache),
+                                  _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
+                                  _ptr(inv_freq), _i32(rows), _i32(q_heads), _i32(key_heads), _i32(value_heads), _i32(dim),
+                                  _i32(vdim), _i32(rot_dims), _i32(page_size), _i32(_code(proj.dtype)), _stream()),
+           "pair_rope_cache")
+
+
+def differential_combine(maps: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *, heads: int,
+                         kv_heads: int, vdim: int, lam: float, post: float, eps: float) -> torch.Tensor:
+    """``o = a1 - lam * a2`` per head, over ``sqrt(mean(o^2) + eps)``, times ``post`` and ``sigmoid(gate)``.  ``maps``
+    float32 ``[T, 2 * heads * vdim]`` holds the two maps' outputs as query heads laid out ``[kv head][map][head within
+    the group]``; ``gate`` (or None) and ``out`` ``[T, heads * vdim]`` in the run dtype, laid out by head."""
+    _cuda(maps, gate, out)
+    rows = out.shape[0]
+    _f32_rows(maps, (rows, 2 * heads * vdim), "differential_combine maps are contiguous float32")
+    _need(out.is_contiguous() and tuple(out.shape) == (rows, heads * vdim), "differential_combine out")
+    _need(gate is None or (gate.stride(1) == 1 and tuple(gate.shape) == (rows, heads * vdim) and gate.dtype == out.dtype),
+          "differential_combine gate")
+    lib = load_library("differential")
+    _check(lib.tb_differential_combine(_ptr(maps), _ptr(gate), _i64(gate.stride(0) if gate is not None else 0), _ptr(out),
+                                       _i32(rows), _i32(heads), _i32(kv_heads), _i32(vdim), _f32(lam), _f32(post),
+                                       _f32(eps), _i32(_code(out.dtype)), _stream()), "differential_combine")
+    return out
+
+
+# ----------------------------------------------------------------------------- attention over a latent vector per token
+
+
+def latent_rope_cache(down: torch.Tensor, q: torch.Tensor, q_full: torch.Tensor, cache: torch.Tensor,
+                      weight: torch.Tensor, positions: torch.Tensor, seq_of_row: torch.Tensor, block_table: torch.Tensor,
+                      inv_freq: Optional[torch.Tensor], *, heads: int, dim: int, rank: int, rot_width: int,
+                      rot_dims: int, page_size: int, eps: float) -> None:
+    """``down`` float32 ``[T, rank + rot_width]``: the first ``rank`` numbers over their root mean square times
+    ``weight`` and the rotated rest go into the row's page (``[page, rank + rot_width]`` a page); the rotated parts of the
+    query heads (``q`` ``[T, heads * (dim + rot_width)]``) go into ``q_full`` ``[T, heads * (rank + rot_width)]`` behind
+    each head's first ``rank`` numbers, which this kernel leaves alone."""
+    _cuda(down, q, q_full, cache, weight, positions, seq_of_row, block_table, inv_freq)
+    rows = q.shape[0]
+    _need(down.dtype == torch.float32 and down.stride(1) == 1 and tuple(down.shape) == (rows, rank + rot_width),
+          "latent_rope_cache down")
+    _need(q.stride(1) == 1 and q.shape[1] == heads * (dim + rot_width), "latent_rope_cache q")
+    _need(q_full.stride(1) == 1 and tuple(q_full.shape) == (rows, heads * (rank + rot_width)) and q_full.dtype == q.dtype,
+          "latent_rope_cache q_full")
+    _need(cache.dtype == q.dtype and cache.is_contiguous(), "latent_rope_cache cache dtype")
+    _need(weight.dtype == torch.float32 and weight.numel() == rank and weight.is_contiguous(), "latent_rope_cache weight")
+    if rot_dims:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2
+              and inv_freq.is_contiguous(), "latent_rope_cache inv_freq")
+    for t in (positions, seq_of_row, block_table):
+        _need(t.dtype == torch.int32, "latent_rope_cache metadata must be int32")
+    lib = load_library("latent_rope_cache")
+    _check(lib.tb_latent_rope_cache(_ptr(down), _i64(down.stride(0)), _ptr(q), _i64(q.stride(0)), _ptr(q_full),
+                                    _i64(q_full.stride(0)), _ptr(cache), _ptr(weight), _ptr(positions), _ptr(seq_of_row),
+                                    _ptr(block_table), _i32(block_table.stride(0)), _ptr(inv_freq), _i32(rows), _i32(heads),
+                                    _i32(dim), _i32(rank), _i32(rot_width), _i32(rot_dims), _i32(page_size), _f32(eps),
+                                    _i32(_code(q.dtype)), _stream()), "latent_rope_cache")

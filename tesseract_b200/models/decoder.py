@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS, Block, CacheBinding, DeferredNorm,
+from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS, TOKEN_INPUTS, Block, CacheBinding, DeferredNorm,
                      ResidualStream, Runtime, StepContext)
 from ..weights.loader import ExpectedTensor
 
@@ -35,6 +35,10 @@ def _part_specs(spec: ModelSpec):
         yield MIXERS, layer.mixer
         if layer.feed_forward is not None:
             yield FEED_FORWARDS, layer.feed_forward
+        if layer.token_input is not None:
+            if not block_cls.accepts_token_input:
+                raise ValueError(f"block '{layer.block}' takes no token input")
+            yield TOKEN_INPUTS, layer.token_input
     for injection in spec.injections:
         yield INJECTIONS, injection
     yield NORMS, spec.final_norm
@@ -83,7 +87,10 @@ class DecoderModel:
             norms = {role: build(NORMS, part) for role, part in layer.norms.items()}
             mixer = build(MIXERS, layer.mixer)
             feed_forward = build(FEED_FORWARDS, layer.feed_forward) if layer.feed_forward is not None else None
-            self.layers.append(block_cls(norms, mixer, feed_forward))
+            if layer.token_input is not None:
+                self.layers.append(block_cls(norms, mixer, feed_forward, token_input=build(TOKEN_INPUTS, layer.token_input)))
+            else:
+                self.layers.append(block_cls(norms, mixer, feed_forward))
         self.injections = [build(INJECTIONS, part) for part in spec.injections]
         self.final_norm = build(NORMS, spec.final_norm)
         # A head that names the embedding's checkpoint tensor (tied embeddings) gets the same host tensor, and the
@@ -117,7 +124,9 @@ class DecoderModel:
         stream = ResidualStream(hidden, None)
         order = self.spec.run_order
         # the embedding output that injections read: rows of their own, since blocks add into the stream in place
-        origin = self.embedding.forward(ctx.token_ids[:ctx.num_rows]) if self.injections else None
+        origin = None
+        if any(injection.reads_origin for injection in self.injections):
+            origin = self.embedding.forward(ctx.token_ids[:ctx.num_rows])
         wants_logits = want_rows is not None and want_rows.numel() > 0
         every_row = wants_logits and want_every_row and want_rows.numel() == ctx.num_rows
         for index, entry in enumerate(order):

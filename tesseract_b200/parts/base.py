@@ -28,6 +28,8 @@ Kinds and what each must provide:
 ``Injection``
     ``forward(stream, origin, ctx)`` -> the new :class:`ResidualStream`: a step between two blocks that mixes the
     stream with the embedding output.
+``TokenInput``
+    ``forward(residual, ctx)``: a term a layer adds to the 32-bit stream behind its sublayers, from the step's tokens.
 
 Every class also has ``expected_tensors(spec)`` -> ``{checkpoint name: ExpectedTensor}``
 so that the loader can check a checkpoint, and the random-weights writer can make one,
@@ -171,9 +173,12 @@ class PagedKeyValueNeed(PagedNeed):
     value_dim: int = 0
     window: Optional[int] = None
     block: Optional[int] = None
+    # value heads, where they are fewer than key heads (several score maps over one set of values); None: as many
+    num_value_heads: Optional[int] = None
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
-        return (self.num_kv_heads * page_size * (self.key_dim + self.value_dim),)
+        value_heads = self.num_kv_heads if self.num_value_heads is None else self.num_value_heads
+        return (page_size * (self.num_kv_heads * self.key_dim + value_heads * self.value_dim),)
 
     def first_needed_position(self, next_position: int) -> int:
         first = PagedNeed.first_needed_position(self, next_position)
@@ -185,6 +190,18 @@ class PagedKeyValueNeed(PagedNeed):
         spans = [s for s in (self.window - 1 if self.window else None, self.block - 1 if self.block else None)
                  if s is not None]
         return min(spans) if spans else None
+
+
+@dataclass(frozen=True)
+class PagedVectorNeed(PagedNeed):
+    """One vector of ``width`` numbers per token (a latent from which keys and values are derived, say): a page is
+    ``[page_size, width]``.  ``window``: only the last ``window`` tokens are read."""
+
+    width: int = 0
+    window: Optional[int] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (page_size * self.width,)
 
 
 @dataclass(frozen=True)
@@ -416,7 +433,18 @@ class Injection(Part):
     the rows as the embedding left them, never written afterwards): ``forward(stream, origin, ctx)`` returns the new
     stream.  The model description says in front of which run entries one stands."""
 
+    # False if ``forward`` never reads ``origin``: a model whose injections all say so keeps no copy of it
+    reads_origin = True
+
     def forward(self, stream: "ResidualStream", origin: torch.Tensor, ctx: StepContext) -> "ResidualStream":
+        raise NotImplementedError
+
+
+class TokenInput(Part):
+    """What a layer adds to the stream for the token itself, behind its sublayers: ``forward(residual, ctx)`` adds to
+    the 32-bit ``residual`` in place (the step's token ids are ``ctx.token_ids``)."""
+
+    def forward(self, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -432,6 +460,9 @@ class Block:
     # True if ``forward`` takes ``next_norm`` (the norm that will consume the stream this block returns) and may
     # return a stream whose ``prepared`` is set for it.
     accepts_next_norm = False
+
+    # True if the constructor takes ``token_input`` (a :class:`TokenInput` that runs behind the sublayers)
+    accepts_token_input = False
 
     def __init__(self, norms: Mapping[str, Norm], mixer: Mixer, feed_forward: Optional[FeedForward]):
         self.norms = dict(norms)
@@ -459,3 +490,4 @@ BLOCKS: Registry[Block] = Registry("block")
 EMBEDDINGS: Registry[Embedding] = Registry("embedding")
 HEADS: Registry[Head] = Registry("head")
 INJECTIONS: Registry[Injection] = Registry("injection")
+TOKEN_INPUTS: Registry[TokenInput] = Registry("token input")

@@ -22,11 +22,20 @@ both results:
 
 Two RMS norms of one row share the row's statistic, so where both norms say so (``shared_statistic``) the pending
 sum and both norms are one kernel.  A layer without a feed-forward leaves (x, a).
+
+``sandwich`` norms every sublayer on both sides, over a stream kept in 32-bit:
+
+    x <- x + post_mixer(mixer(pre_mixer(x)))
+    x <- x + post_feed_forward(feed_forward(pre_feed_forward(x)))       (absent without a feed-forward)
+    x <- x + token_input(x, tokens)                                     (absent without a token input)
+
+The norm of a sublayer's result, the addition and the norm in front of the next sublayer are one kernel
+(``norm_add_norm``); it also leaves the rounded stream that the token input's first product reads.
 """
 
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Mapping, Optional, Tuple
 
 from .base import (BLOCKS, Block, CacheBinding, DeferredNorm, FollowNorm, Norm, PreparedNorm, ResidualStream,
                    StepContext)
@@ -108,3 +117,61 @@ class ParallelBlock(Block):
         if self.feed_forward is None:
             return ResidualStream(stream.residual, mixed)
         return ResidualStream(stream.residual, mixed, update_b=self.feed_forward.forward(x_feed, ctx))
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """Norm roles: ``pre_mixer``, ``post_mixer`` and, with a feed-forward, ``pre_feed_forward``, ``post_feed_forward``.
+    Every norm offers ``norm_parameters()`` (what ``kernels.norm_add_norm`` takes) and ``eps``; all share one ``eps``."""
+
+    accepts_token_input = True
+
+    def __init__(self, norms, mixer, feed_forward, token_input=None):
+        super().__init__(norms, mixer, feed_forward)
+        self.token_input = token_input
+        for role, norm in self.norms.items():
+            if not hasattr(norm, "norm_parameters"):
+                raise ValueError(f"a sandwich block's norms describe themselves to the fused kernel; '{norm.kind}' ({role}) does not")
+        if len({norm.eps for norm in self.norms.values()}) != 1:
+            raise ValueError("the norms of a sandwich block share one eps")
+        self.eps = next(iter(self.norms.values())).eps
+
+    @classmethod
+    def norm_roles(cls, with_feed_forward: bool = True) -> Tuple[str, ...]:
+        both = ("pre_mixer", "post_mixer", "pre_feed_forward", "post_feed_forward")
+        return both if with_feed_forward else both[:2]
+
+    def entry_norm(self) -> Optional[Norm]:
+        return self.norms["pre_mixer"]
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache) -> ResidualStream:
+        import torch
+
+        from .. import kernels
+
+        if stream.prepared is not None or stream.update_b is not None:
+            raise NotImplementedError("a sandwich block takes the stream as a residual and at most one pending update")
+        residual = stream.residual
+        if residual.dtype != torch.float32:
+            raise NotImplementedError("a sandwich block keeps its stream in 32-bit")
+        dtype = self.mixer.runtime.dtype
+
+        def rows_like():
+            return torch.empty(residual.shape, dtype=dtype, device=residual.device)
+
+        x = rows_like()
+        kernels.norm_add_norm(residual, stream.update, None, self.norms["pre_mixer"].norm_parameters(), x, None, self.eps)
+        mixed = self.mixer.forward(x, ctx, cache)
+        wants_copy = self.token_input is not None and dtype != torch.float32
+        if self.feed_forward is not None:
+            x = rows_like()
+            kernels.norm_add_norm(residual, mixed, self.norms["post_mixer"].norm_parameters(),
+                                  self.norms["pre_feed_forward"].norm_parameters(), x, None, self.eps)
+            update, post = self.feed_forward.forward(x, ctx), self.norms["post_feed_forward"]
+        else:
+            update, post = mixed, self.norms["post_mixer"]
+        copy = rows_like() if wants_copy else None
+        kernels.norm_add_norm(residual, update, post.norm_parameters(), None, None, copy, self.eps)
+        if self.token_input is not None:
+            self.token_input.forward(residual, ctx, rounded=copy if wants_copy else residual)
+        return ResidualStream(residual, None)

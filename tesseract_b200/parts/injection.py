@@ -55,3 +55,37 @@ class OriginMix(Injection):
         both = torch.empty((residual.shape[0], 2 * self.hidden_size), dtype=self.runtime.dtype, device=residual.device)
         kernels.sum_concat(residual, first, second, origin, both)
         return ResidualStream(self.proj.forward(both, float32_out=True))
+
+
+@INJECTIONS.register("stream_bias")
+class StreamBias(Injection):
+    """``x <- x + table[row]``: a learned vector added to the 32-bit stream (every walk of a run of layers that is
+    walked several times starts with one of its own).  params: ``hidden_size``, ``rows``, ``row``; weights: ``table``
+    ``[rows, hidden]`` (one tensor for all walks; kept in 32-bit)."""
+
+    graph_safe = True
+    reads_origin = False
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        self.hidden_size = int(spec.params["hidden_size"])
+        row, rows = int(spec.params["row"]), int(spec.params["rows"])
+        if not 0 <= row < rows:
+            raise ValueError(f"row {row} of a table of {rows}")
+        self.vector = runtime.vector_f32(tensors["table"])[row].contiguous()
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
+        return {spec.weights["table"]: ExpectedTensor((int(spec.params["rows"]), int(spec.params["hidden_size"])))}
+
+    @classmethod
+    def random_tensor(cls, spec, role, shape, generator) -> torch.Tensor:
+        return torch.randn(shape, generator=generator, dtype=torch.float32) * 0.3
+
+    def forward(self, stream: ResidualStream, origin, ctx: StepContext) -> ResidualStream:
+        if stream.prepared is not None or stream.update is not None or stream.update_b is not None:
+            raise NotImplementedError("stream_bias takes a stream without pending updates")
+        if stream.residual.dtype != torch.float32:
+            raise NotImplementedError("stream_bias adds to a 32-bit stream")
+        kernels.add_bias(stream.residual, self.vector)
+        return stream

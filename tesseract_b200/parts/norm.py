@@ -115,3 +115,52 @@ class GroupedRMSNorm(Norm):
     def forward_add(self, residual: torch.Tensor, update: torch.Tensor,
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
         return kernels.group_rms_norm(residual, update, self.weight, self.groups, self.eps, self._out(residual, out))
+
+
+@NORMS.register("layer_norm")
+class LayerNorm(Norm):
+    """Layer norm with weight and bias over a residual stream kept in 32-bit: ``(x - mean) / sqrt(var + eps) * weight +
+    bias``, ``var`` the mean of the squared deviations.
+
+    params: ``size``, ``eps``; weights: ``weight``, ``bias`` (``[size]`` each, kept in 32-bit).  The stream (``x`` /
+    ``residual``) and an update are float32 whatever the run dtype; the normalised rows come out in the run dtype,
+    rounded once.  ``norm_parameters()`` hands a block the kernel's description of this norm, so that the block may
+    run it together with the addition in front (a sublayer whose result is normed before it joins the stream)."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        params = spec.params
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.weight = runtime.vector_f32(tensors["weight"])
+        self.bias = runtime.vector_f32(tensors["bias"])
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
+        size = int(spec.params["size"])
+        return {spec.weights["weight"]: ExpectedTensor((size,)), spec.weights["bias"]: ExpectedTensor((size,))}
+
+    @classmethod
+    def random_tensor(cls, spec, role, shape: Tuple[int, ...], generator) -> torch.Tensor:
+        noise = torch.randn(shape, generator=generator, dtype=torch.float32) * 0.1
+        return noise if role == "bias" else 1.0 + noise
+
+    def norm_parameters(self):
+        """``(kind, weight, bias)`` as ``kernels.norm_add_norm`` takes a norm."""
+        return (kernels.NORM_LAYER, self.weight, self.bias)
+
+    def _out(self, x: torch.Tensor, out: Optional[torch.Tensor]) -> torch.Tensor:
+        return out if out is not None else torch.empty(x.shape, dtype=self.runtime.dtype, device=x.device)
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        out = self._out(x, out)
+        kernels.norm_add_norm(x, None, None, self.norm_parameters(), out, None, self.eps)
+        return out
+
+    def forward_add(self, residual: torch.Tensor, update: torch.Tensor,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        out = self._out(residual, out)
+        kernels.norm_add_norm(residual, update, None, self.norm_parameters(), out, None, self.eps)
+        return out

@@ -67,14 +67,37 @@ class RotaryEncoding(PositionEncoding):
         raise NotImplementedError("rotary encoding is applied by the attention mixer's fused rotate-and-store kernel")
 
 
+def banded_inverse_frequencies(dims: int, base: float, scaling: Optional[Mapping[str, float]]) -> np.ndarray:
+    """float64 ``[dims / 2]``: ``f_i = base^(-2i / dims)`` and, with ``scaling`` (``factor``, ``low``, ``high``,
+    ``original``), three bands by wavelength ``l = 2 pi / f``: short ones (``l < original / high``) keep ``f``, long ones
+    (``l > original / low``) take ``f / factor``, and between them ``(1 - s) f / factor + s f`` with
+    ``s = (original / l - low) / (high - low)``."""
+    out = np.asarray([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=np.float64)
+    if not scaling:
+        return out
+    factor, low, high = float(scaling["factor"]), float(scaling["low"]), float(scaling["high"])
+    original = float(scaling["original"])
+    for i, f in enumerate(out):
+        wavelength = 2.0 * math.pi / f
+        if wavelength < original / high:
+            continue
+        if wavelength > original / low:
+            out[i] = f / factor
+        else:
+            s = (original / wavelength - low) / (high - low)
+            out[i] = (1.0 - s) * f / factor + s * f
+    return out
+
+
 @POSITION_ENCODINGS.register("rotary_pairs")
 class RotaryPairs(PositionEncoding):
     """Rotation of neighbouring pairs: of every head's first ``dims`` numbers, numbers ``2i`` and ``2i + 1`` turn by
     ``position * base^(-2i / dims)``; the rest of the head passes unchanged.
 
-    params: ``head_dim``, ``dims`` (even, at most ``head_dim``), ``base``.  The frequencies are taken in 64-bit on
+    params: ``head_dim``, ``dims`` (even, at most ``head_dim``), ``base``, optional ``scaling`` (mapping with ``factor``,
+    ``low``, ``high``, ``original``: :func:`banded_inverse_frequencies`).  The frequencies are taken in 64-bit on
     the host and rounded once to 32-bit; the angle and its sine and cosine are 32-bit, in the kernel that applies
-    them (the mixer's convolve-rotate-and-store kernel reads ``pair_inv_freq`` and ``dims``)."""
+    them (the mixer's rotate-and-store kernel reads ``pair_inv_freq`` and ``dims``)."""
 
     def __init__(self, spec: PartSpec, tensors, runtime: Runtime):
         super().__init__(spec, tensors, runtime)
@@ -86,8 +109,8 @@ class RotaryPairs(PositionEncoding):
             raise ValueError(f"rotation over pairs needs an even number of dimensions up to {self.head_dim}, got {self.dims}")
         if not self.base > 0.0:
             raise ValueError("the rotation's base must be positive")
-        self.inv_freq_host = np.asarray([self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)],
-                                        dtype=np.float64).astype(np.float32)
+        scaling = params.get("scaling")
+        self.inv_freq_host = banded_inverse_frequencies(self.dims, self.base, dict(scaling) if scaling else None).astype(np.float32)
         self.pair_inv_freq = torch.from_numpy(self.inv_freq_host).to(runtime.device) if self.dims else None
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
