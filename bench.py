@@ -664,7 +664,7 @@ def run_kernels(args):
 
 
 # ----------------------------------------------------------------------------- another design beside Llama
-# `--design revesun|pekodra`: prefill and decode of a model of that design at layer sizes like a real model's (random
+# `--design revesun|pekodra|kazodra`: prefill and decode of a model of that design at layer sizes like a real model's (random
 # weights), beside a Llama (and, for Pekodra, a Revesun: the other design with a 32-bit stream) of the same width, heads, head sizes, layer count and about as many weights a layer, measured the
 # same way; then the design's own kernels alone, against the bytes they must move.  The default workload is untouched.
 DESIGN_SIZES = {
@@ -716,6 +716,47 @@ def pekodra_config(size, layers):
     config = {"architecture": "Pekodra", "torch_dtype": "bfloat16", "width": z["width"], "vocab": DESIGN_VOCAB,
               "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
               "layers": [{"type": "attention", "mixer": mixer, "mlp": moe if i % 2 else dense} for i in range(stored)]}
+    if stop > start:
+        config["loop"] = {"start": start, "stop": stop, "times": 2}
+    return config
+
+
+KAZODRA_SIZES = {
+    # (the layers run: `stored` of them, the run `looped` walked twice, are as many as the models beside it run; the
+    # stored layers go lightning, lightning, two-map attention, latent attention, and over again)
+    "1b": dict(heads=16, kv_heads=4, dim=64, vdim=128, window=512, rank=512, rot=64, latent_heads=16, latent_dim=128,
+               light_heads=16, light_dim=128, ff=8192, side=128, stored=10, looped=(2, 8)),
+    "3b": dict(heads=12, kv_heads=4, dim=128, vdim=128, window=512, rank=512, rot=64, latent_heads=24, latent_dim=128,
+               light_heads=24, light_dim=128, ff=8192, side=128, stored=8, looped=(2, 6)),
+    "8b": dict(heads=16, kv_heads=4, dim=128, vdim=128, window=512, rank=512, rot=64, latent_heads=32, latent_dim=128,
+               light_heads=32, light_dim=128, ff=14336, side=256, stored=5, looped=(1, 4)),
+}
+
+
+def kazodra_config(size, layers):
+    """Two layers of linear attention with a decay, one of attention with two score maps, one of attention over a
+    latent under a window, and so on; every layer has a dense feed-forward and a token input; a run in the middle is
+    walked twice, so that `layers` layer runs happen in all (as many as the models beside it run)."""
+    z, p = DESIGN_SIZES[size], KAZODRA_SIZES[size]
+    stored, (start, stop) = p["stored"], p["looped"]
+    if layers != z["layers"]:                      # another layer count: no loop, one stored layer a run
+        stored, start, stop = layers, 0, 0
+    heads = p["light_heads"]
+    decay = [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, heads - 1)) for h in range(heads)]
+    lightning = {"type": "lightning", "mixer": {"heads": heads, "dim": p["light_dim"], "vdim": p["light_dim"], "decay": decay}}
+    two_maps = {"type": "attention",
+                "mixer": {"heads": p["heads"], "kv_heads": p["kv_heads"], "dim": p["dim"], "vdim": p["vdim"], "diff": 0.8,
+                          "scale": p["dim"] ** -0.5,
+                          "rot": {"dims": p["dim"], "base": 500000.0,
+                                  "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": p["latent_heads"], "dim": p["latent_dim"], "rot_dim": p["rot"], "vdim": p["latent_dim"],
+                        "kv_rank": p["rank"], "mask": {"size": p["window"]}, "scale": (p["latent_dim"] + p["rot"]) ** -0.5,
+                        "rot": {"dims": p["rot"], "base": 10000.0}}}
+    order = [lightning, lightning, two_maps, latent]
+    config = {"architecture": "Kazodra", "torch_dtype": "bfloat16", "width": z["width"], "vocab": DESIGN_VOCAB,
+              "norm": {"eps": 1e-5}, "token_side": {"dim": p["side"]},
+              "layers": [dict(order[i % 4], mlp={"kind": "dense", "ff": p["ff"]}) for i in range(stored)]}
     if stop > start:
         config["loop"] = {"start": start, "stop": stop, "times": 2}
     return config
@@ -803,10 +844,22 @@ def run_design(args):
         scratch.cleanup()
         return out
 
-    result = {"design": {"revesun": "Revesun", "pekodra": "Pekodra"}[args.design], "size": args.size, "layers": layers,
+    result = {"design": {"revesun": "Revesun", "pekodra": "Pekodra", "kazodra": "Kazodra"}[args.design], "size": args.size,
+              "layers": layers,
               "vocab": DESIGN_VOCAB, "dtype": "bf16", "data": "synthetic",
               "l2": "a 256 MB buffer is written between timed prefill steps; a decode step reads its weights, which "
                     "exceed L2"}
+    if args.design == "kazodra":                   # beside Pekodra, the other design with a 32-bit stream and a loop
+        if args.only in ("all", "decode", "prefill"):
+            result["kazodra"] = measure(kazodra_config(args.size, layers))
+            result["pekodra"] = measure(pekodra_config(args.size, layers))
+            result["llama"] = measure(llama)
+        if args.only in ("all", "kernels"):
+            result["kernels"] = kazodra_kernels(args.size, pk)
+        result["clocks"] = sampler.stop(windows)
+        result["peaks"] = pk
+        print(json.dumps(result))
+        return 0
     if args.design == "pekodra":
         result["pekodra"] = measure(pekodra_config(args.size, layers))
     result["revesun"] = measure(revesun_config(args.size, layers))
@@ -926,6 +979,187 @@ def design_kernels(size, pk):
             return lambda: kernels.polynorm(x, c, 1e-5, x)
 
         timed(f"polynorm/{label}", act, rows * F * 2 * 2)
+    return out
+
+
+def kazodra_kernels(size, pk):
+    """Kazodra's own kernels alone at this size, timed like :func:`design_kernels`: 2,048 prompt rows of one sequence,
+    and 64 and 8 decoded rows at context 2,048."""
+    import torch
+
+    from tesseract_b200 import kernels
+
+    z, p = DESIGN_SIZES[size], KAZODRA_SIZES[size]
+    dev = "cuda"
+    W, page = z["width"], PAGE_SIZE
+    H, G, d, dv = p["heads"], p["kv_heads"], p["dim"], p["vdim"]
+    LH, ld, rank, rot, window = p["latent_heads"], p["latent_dim"], p["rank"], p["rot"], p["window"]
+    NH, nd = p["light_heads"], p["light_dim"]
+    side = p["side"]
+    entry = rank + rot
+    pair_freq = torch.tensor([5e5 ** (-2.0 * i / d) for i in range(d // 2)], dtype=torch.float32, device=dev)
+    rot_freq = torch.tensor([1e4 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32, device=dev)
+    SETS = 8
+    out = {}
+
+    def timed(name, make, nbytes, flops=0, tensor=False):
+        runs = [make(k) for k in range(SETS)]
+        torch.cuda.synchronize()
+        side_stream = torch.cuda.Stream()
+        with torch.cuda.stream(side_stream):
+            for run in runs:
+                run()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()                 # one graph of the eight launches: no host time between them
+        with torch.cuda.graph(graph):
+            for run in runs:
+                run()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / SETS)
+        us = statistics.median(times)
+        line = {"us": round(us, 2), "mb": round(nbytes / 1e6, 2), "gbs": round(nbytes / us / 1e3, 1),
+                "frac_of_measured_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if flops:
+            line["tflops"] = round(flops / us / 1e6, 2)
+            if tensor:
+                line["frac_of_measured_bf16"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
+        out[name] = line
+
+    for label, rows, seqs, begin in (("prefill_2048", 2048, 1, 0), ("decode_64", 64, 64, 2047), ("decode_8", 8, 8, 2047)):
+        new = rows // seqs
+        positions = (torch.arange(rows, dtype=torch.int32, device=dev) % new) + begin
+        seq_of_row = torch.arange(rows, dtype=torch.int32, device=dev) // new
+        row_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * new
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        pages_per_seq = 2048 // page
+        table = (torch.arange(seqs * pages_per_seq, dtype=torch.int32, device=dev) + 1).view(seqs, pages_per_seq)
+        vector = lambda: (torch.ones(W, device=dev), torch.zeros(W, device=dev))          # noqa: E731
+
+        def norms(k):
+            res, upd = torch.randn(rows, W, device=dev), torch.randn(rows, W, device=dev)
+            (w1, b1), (w2, b2) = vector(), vector()
+            y = torch.empty(rows, W, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.norm_add_norm(res, upd, (kernels.NORM_LAYER, w1, b1), (kernels.NORM_LAYER, w2, b2), y,
+                                                 None, 1e-5)
+
+        timed(f"norm_add_norm (norm, add, norm)/{label}", norms, rows * W * (4 * 3 + 2))
+
+        def gated_norm(k):
+            v = torch.randn(rows, NH * nd, device=dev)
+            w = torch.ones(NH * nd, device=dev)
+            gate = torch.randn(rows, NH * nd, device=dev).bfloat16()
+            y = torch.empty(rows, NH * nd, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.gated_rms_norm(v, w, gate, y, 1e-5)
+
+        timed(f"gated_rms_norm/{label}", gated_norm, rows * NH * nd * (4 + 2 + 2))
+
+        def token_gate(k):
+            zed = torch.randn(rows, side, device=dev)
+            tokens = torch.randint(0, DESIGN_VOCAB, (rows,), dtype=torch.int32, device=dev)
+            table_side = torch.randn(DESIGN_VOCAB, 4 * side, device=dev).bfloat16()
+            y = torch.empty(rows, side, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.token_gate(zed, tokens, table_side, side * (k % 4), y, kernels.ACT_GELU_TANH)
+
+        timed(f"token_gate/{label}", token_gate, rows * side * (4 + 2 + 2))
+
+        def recurrence(k):
+            proj = torch.randn(rows, NH * 4 * nd, device=dev).bfloat16()
+            decay = torch.full((NH,), 0.99, device=dev)
+            state = torch.zeros(seqs + 1, NH, nd, nd, device=dev)
+            y = torch.empty(rows, NH * nd, device=dev)
+            return lambda: kernels.lightning(proj, decay, state, y, row_start, slots, num_seqs=seqs, heads=NH, dim=nd,
+                                             vdim=nd, max_new=new)
+
+        timed(f"lightning/{label}", recurrence, rows * NH * nd * (3 * 2 + 4) + seqs * NH * nd * nd * 8,
+              flops=rows * NH * 4 * nd * nd)
+
+        channels = 2 * H * d + 2 * G * d + G * dv
+        page_elems = page * (2 * G * d + G * dv)
+
+        def rotate(k):
+            proj = torch.randn(rows, channels + H * dv, device=dev).bfloat16()
+            q = torch.empty(rows, 2 * H * d, dtype=torch.bfloat16, device=dev)
+            cache = torch.zeros(seqs * pages_per_seq + 1, page_elems, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.pair_rope_cache(proj, q, cache, positions, seq_of_row, table, pair_freq, q_heads=2 * H,
+                                                   key_heads=2 * G, value_heads=G, dim=d, vdim=dv, rot_dims=d,
+                                                   page_size=page)
+
+        timed(f"pair_rope_cache/{label}", rotate, rows * channels * 2 * 2)
+
+        causal_keys = sum(int(q) + 1 for q in positions.tolist())
+        kv_read = (2048 if new > 1 else seqs * (begin + 1)) * (2 * G * d + G * dv) * 2
+
+        def two_maps(k):
+            q = torch.randn(rows, 2 * H * d, device=dev).bfloat16()
+            maps = torch.empty(rows, 2 * H * dv, device=dev)
+            cache = torch.randn(seqs * pages_per_seq + 1, page_elems, device=dev).bfloat16()
+            return lambda: kernels.attention_masked(q, None, maps, cache, positions, seq_of_row, table, heads=2 * H,
+                                                    kv_heads=2 * G, dim=d, vdim=dv, page_size=page,
+                                                    mask_kind=kernels.MASK_CAUSAL, mask_size=0, sink=False,
+                                                    scale=d ** -0.5, keys_per_value=2)
+
+        timed(f"attention_masked (two maps, causal)/{label}", two_maps, rows * 2 * H * (d * 2 + dv * 4) + kv_read,
+              flops=causal_keys * 2 * H * 2 * (d + dv))
+
+        def two_maps_mma(k):
+            q = torch.randn(rows, 2 * H * d, device=dev).bfloat16()
+            maps = torch.empty(rows, 2 * H * dv, device=dev)
+            cache = torch.randn(seqs * pages_per_seq + 1, page_elems, device=dev).bfloat16()
+            common = dict(heads=2 * H, kv_heads=2 * G, dim=d, vdim=dv, page_size=page, mask_kind=kernels.MASK_CAUSAL,
+                          mask_size=0, scale=d ** -0.5, keys_per_value=2)
+            if new > 1:
+                return lambda: kernels.attention_prompt_mma(q, maps, cache, positions, row_start, table, num_seqs=seqs,
+                                                            **common)
+            return lambda: kernels.attention_rows_mma(q, maps, cache, positions, seq_of_row, table, **common)
+
+        if kernels.attention_prompt_mma_supported(torch.bfloat16, d, dv):
+            timed(f"{'attention_prompt_mma' if new > 1 else 'attention_rows_mma'} (two maps, causal)/{label}", two_maps_mma,
+                  rows * 2 * H * (d * 2 + dv * 4) + kv_read, flops=causal_keys * 2 * H * 2 * (d + dv), tensor=new > 1)
+
+        def combine(k):
+            maps = torch.randn(rows, 2 * H * dv, device=dev)
+            gate = torch.randn(rows, H * dv, device=dev).bfloat16()
+            y = torch.empty(rows, H * dv, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.differential_combine(maps, gate, y, heads=H, kv_heads=G, vdim=dv, lam=0.5, post=0.2,
+                                                        eps=1e-5)
+
+        timed(f"differential_combine/{label}", combine, rows * H * dv * (8 + 2 + 2))
+
+        def latent_write(k):
+            down = torch.randn(rows, entry, device=dev)
+            q = torch.randn(rows, LH * (ld + rot), device=dev).bfloat16()
+            q_full = torch.empty(rows, LH * entry, dtype=torch.bfloat16, device=dev)
+            w = torch.ones(rank, device=dev)
+            cache = torch.zeros(seqs * pages_per_seq + 1, page * entry, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.latent_rope_cache(down, q, q_full, cache, w, positions, seq_of_row, table, rot_freq,
+                                                     heads=LH, dim=ld, rank=rank, rot_width=rot, rot_dims=rot,
+                                                     page_size=page, eps=1e-5)
+
+        timed(f"latent_rope_cache/{label}", latent_write, rows * (entry * (4 + 2) + LH * rot * 2 * 2))
+
+        window_keys = sum(min(int(q), window - 1) + 1 for q in positions.tolist())
+        latent_read = (2048 if new > 1 else seqs * min(begin + 1, window)) * entry * 2
+
+        def latent_attend(k):
+            q_full = torch.randn(rows, LH * entry, device=dev).bfloat16()
+            mixed = torch.empty(rows, LH * rank, dtype=torch.bfloat16, device=dev)
+            cache = torch.randn(seqs * pages_per_seq + 1, page * entry, device=dev).bfloat16()
+            return lambda: kernels.attention_masked(q_full, None, mixed, cache, positions, seq_of_row, table, heads=LH,
+                                                    kv_heads=1, dim=entry, vdim=rank, page_size=page,
+                                                    mask_kind=kernels.MASK_WINDOW, mask_size=window, sink=False,
+                                                    scale=(ld + rot) ** -0.5, keys_per_value=0)
+
+        timed(f"attention_masked (latent, window {window})/{label}", latent_attend,
+              rows * LH * (entry + rank) * 2 + latent_read, flops=window_keys * LH * 2 * (entry + rank))
     return out
 
 
@@ -1131,7 +1365,7 @@ def main():
     parser.add_argument("--workload", choices=["3b", "8b"], default=None,
                         help="run another workload instead of the headline one: continuous batching at the 3B sizes, "
                              "or a 2,048-token portion beside 64 decode rows at the 8B sizes")
-    parser.add_argument("--design", choices=["revesun", "pekodra"], default=None,
+    parser.add_argument("--design", choices=["revesun", "pekodra", "kazodra"], default=None,
                         help="instead of the headline workload: prefill and decode of this design beside a Llama of "
                              "equal layer sizes (--size), and the design's own kernels alone")
     args = parser.parse_args()

@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(128)
 attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ out, int64_t out_stride,
                         const bf16* __restrict__ cache, const int* __restrict__ positions,
                         const int* __restrict__ row_start, const int* __restrict__ block_table, int bt_stride,
-                        int num_seqs, int heads, int kv_heads, int page_size, int mask_kind, int mask_size, float scale) {
+                        int num_seqs, int heads, int kv_heads, int page_size, int mask_kind, int mask_size, float scale,
+                        int keys_per_value, int out_f32) {
     constexpr int KS = D * 2 + 16, VS = DV * 2 + 16;              // bytes of a key row and a value row in shared memory
     constexpr int STAGE = KT * (KS + VS);
     extern __shared__ __align__(128) unsigned char tile_smem[];   // two stages of keys then values
@@ -91,9 +92,10 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
     const int pos_first = positions[r0], pos_last = pos_first + n - 1;        // a sequence's rows stand at consecutive positions
     const int key_lo = first_key_of(pos_first, mask_kind, mask_size);
     const int tiles = (pos_last - key_lo) / KT + 1;
-    const int64_t page_elems = (int64_t)kv_heads * page_size * (D + DV);
+    // keys_per_value key heads in a row read one value head: the page holds kv_heads / keys_per_value of those
+    const int64_t page_elems = (int64_t)kv_heads * page_size * D + (int64_t)(kv_heads / keys_per_value) * page_size * DV;
     const bf16* kbase = cache + (int64_t)kv_head * page_size * D;
-    const bf16* vbase = cache + (int64_t)kv_heads * page_size * D + (int64_t)kv_head * page_size * DV;
+    const bf16* vbase = cache + (int64_t)kv_heads * page_size * D + (int64_t)(kv_head / keys_per_value) * page_size * DV;
     const int* table = block_table + (int64_t)seq * bt_stride;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(tile_smem);
 
@@ -247,6 +249,13 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
         if (!there[r]) continue;
         const float inv = 1.0f / fmaxf(l[r], 1.0e-30f);
+        if (out_f32) {                                            // the weighted sums as they are, unrounded
+            float* orow = reinterpret_cast<float*>(out) + (int64_t)(r0 + i0 + g + r * 8) * out_stride + (int64_t)head * DV;
+#pragma unroll
+            for (int j = 0; j < DV / 8; ++j)
+                *reinterpret_cast<float2*>(orow + j * 8 + 2 * t) = make_float2(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+            continue;
+        }
         bf16* orow = out + (int64_t)(r0 + i0 + g + r * 8) * out_stride + (int64_t)head * DV;
 #pragma unroll
         for (int j = 0; j < DV / 8; ++j)
@@ -263,7 +272,8 @@ __global__ void __launch_bounds__(128)
 attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ out, int64_t out_stride,
                       const bf16* __restrict__ cache, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride, int heads,
-                      int kv_heads, int page_size, int mask_kind, int mask_size, float scale) {
+                      int kv_heads, int page_size, int mask_kind, int mask_size, float scale, int keys_per_value,
+                      int out_f32) {
     constexpr int KS = D * 2 + 16, VS = DV * 2 + 16;
     constexpr int STAGE = KT * (KS + VS);
     constexpr int PART = DV + 2;                                  // a row's accumulator, maximum and sum
@@ -275,9 +285,10 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
     const int pos = positions[row], seq = seq_of_row[row];
     const int key_lo = first_key_of(pos, mask_kind, mask_size);
     const int tiles = (pos - key_lo) / KT + 1;
-    const int64_t page_elems = (int64_t)kv_heads * page_size * (D + DV);
+    // keys_per_value key heads in a row read one value head: the page holds kv_heads / keys_per_value of those
+    const int64_t page_elems = (int64_t)kv_heads * page_size * D + (int64_t)(kv_heads / keys_per_value) * page_size * DV;
     const bf16* kbase = cache + (int64_t)kv_head * page_size * D;
-    const bf16* vbase = cache + (int64_t)kv_heads * page_size * D + (int64_t)kv_head * page_size * DV;
+    const bf16* vbase = cache + (int64_t)kv_heads * page_size * D + (int64_t)(kv_head / keys_per_value) * page_size * DV;
     const int* table = block_table + (int64_t)seq * bt_stride;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(tile_smem);
     const int copy_row = tid >> 1, copy_half = tid & 1;
@@ -428,15 +439,17 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
             total = fmaf(theirs[DV + 1], weight, total);
             value = fmaf(theirs[col], weight, value);
         }
-        out[(int64_t)row * out_stride + (int64_t)(kv_head * per + head_row) * DV + col] =
-            __float2bfloat16_rn(value / fmaxf(total, 1.0e-30f));
+        const int64_t at = (int64_t)row * out_stride + (int64_t)(kv_head * per + head_row) * DV + col;
+        if (out_f32) reinterpret_cast<float*>(out)[at] = value / fmaxf(total, 1.0e-30f);
+        else out[at] = __float2bfloat16_rn(value / fmaxf(total, 1.0e-30f));
     }
 }
 
 template <int D, int DV>
 int launch_rows(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache, const int* positions,
                 const int* seq_of_row, const int* block_table, int bt_stride, int rows, int heads, int kv_heads,
-                int page_size, int mask_kind, int mask_size, float scale, cudaStream_t stream) {
+                int page_size, int mask_kind, int mask_size, float scale, int keys_per_value, int out_f32,
+                cudaStream_t stream) {
     constexpr int smem = 2 * KT * (D * 2 + 16 + DV * 2 + 16) + 4 * 16 * (DV + 2) * 4;
     auto kernel = attention_rows_kernel<D, DV>;
     if (smem > 40 * 1024) {
@@ -445,14 +458,15 @@ int launch_rows(const void* q, int64_t q_stride, void* out, int64_t out_stride, 
     }
     cudaError_t launched = tb_launch_pdl(kernel, dim3(rows, kv_heads), dim3(128), (size_t)smem, stream, (const bf16*)q,
                                          q_stride, (bf16*)out, out_stride, (const bf16*)cache, positions, seq_of_row,
-                                         block_table, bt_stride, heads, kv_heads, page_size, mask_kind, mask_size, scale);
+                                         block_table, bt_stride, heads, kv_heads, page_size, mask_kind, mask_size, scale,
+                                         keys_per_value, out_f32);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
 template <int D, int DV>
 int launch(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache, const int* positions,
            const int* row_start, const int* block_table, int bt_stride, int rows, int num_seqs, int heads, int kv_heads,
-           int page_size, int mask_kind, int mask_size, float scale, cudaStream_t stream) {
+           int page_size, int mask_kind, int mask_size, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
     constexpr int smem = 2 * KT * (D * 2 + 16 + DV * 2 + 16);
     auto kernel = attention_prompt_kernel<D, DV>;
     if (smem > 40 * 1024) {
@@ -462,7 +476,8 @@ int launch(const void* q, int64_t q_stride, void* out, int64_t out_stride, const
     const dim3 grid((rows + QT - 1) / QT + num_seqs, heads);
     cudaError_t launched = tb_launch_pdl(kernel, grid, dim3(128), (size_t)smem, stream, (const bf16*)q, q_stride,
                                          (bf16*)out, out_stride, (const bf16*)cache, positions, row_start, block_table,
-                                         bt_stride, num_seqs, heads, kv_heads, page_size, mask_kind, mask_size, scale);
+                                         bt_stride, num_seqs, heads, kv_heads, page_size, mask_kind, mask_size, scale,
+                                         keys_per_value, out_f32);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
@@ -473,16 +488,20 @@ TB_EXPORT int tb_attention_prompt_mma_supported(int dim, int vdim) {
     return ((dim == 64 || dim == 128) && (vdim == 64 || vdim == 128)) || (dim == 64 && vdim == 48) ? 1 : 0;
 }
 
-// q: bfloat16 [rows, heads * dim] (row stride q_stride, elements); out: bfloat16 [rows, heads * vdim]; cache: this
-// layer's pages ([kv_heads][page_size][dim] keys then [kv_heads][page_size][vdim] values a page); row_start: int32
-// [num_seqs + 1]; the rows of a sequence stand at consecutive positions.  mask_kind: 0 causal, 1 window, 2 blocks.
+// q: bfloat16 [rows, heads * dim] (row stride q_stride, elements); out: bfloat16, or with out_f32 float32 (the sums
+// unrounded), [rows, heads * vdim], row stride out_stride in its own elements; cache: this layer's pages
+// ([kv_heads][page_size][dim] keys then [kv_heads / keys_per_value][page_size][vdim] values a page, key head g reading
+// value head g / keys_per_value); row_start: int32 [num_seqs + 1]; the rows of a sequence stand at consecutive
+// positions.  mask_kind: 0 causal, 1 window, 2 blocks.
 TB_EXPORT int tb_attention_prompt_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
                                       const int* positions, const int* row_start, const int* block_table, int bt_stride,
                                       int rows, int num_seqs, int heads, int kv_heads, int dim, int vdim, int page_size,
-                                      int mask_kind, int mask_size, float scale, cudaStream_t stream) {
+                                      int mask_kind, int mask_size, float scale, int keys_per_value, int out_f32,
+                                      cudaStream_t stream) {
     if (rows == 0) return 0;
     if (!tb_attention_prompt_mma_supported(dim, vdim)) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || page_size < 1 || num_seqs < 1) return TB_ERR_BAD_SIZE;
+    if (keys_per_value < 1 || kv_heads % keys_per_value != 0) return TB_ERR_BAD_SIZE;
     if (heads > 65535) return TB_ERR_BAD_SIZE;
     if (mask_kind < MASK_CAUSAL || mask_kind > MASK_BLOCKS) return TB_ERR_BAD_SIZE;
     if (mask_kind != MASK_CAUSAL && mask_size < 1) return TB_ERR_BAD_SIZE;
@@ -490,7 +509,7 @@ TB_EXPORT int tb_attention_prompt_mma(const void* q, int64_t q_stride, void* out
         return TB_ERR_BAD_ALIGN;
 #define TB_ATTEND(D, DV)                                                                                            \
     return launch<D, DV>(q, q_stride, out, out_stride, cache, positions, row_start, block_table, bt_stride, rows,    \
-                         num_seqs, heads, kv_heads, page_size, mask_kind, mask_size, scale, stream)
+                         num_seqs, heads, kv_heads, page_size, mask_kind, mask_size, scale, keys_per_value, out_f32, stream)
     if (dim == 64 && vdim == 48) TB_ATTEND(64, 48);
     if (dim == 64 && vdim == 64) TB_ATTEND(64, 64);
     if (dim == 64 && vdim == 128) TB_ATTEND(64, 128);
@@ -504,17 +523,18 @@ TB_EXPORT int tb_attention_prompt_mma(const void* q, int64_t q_stride, void* out
 TB_EXPORT int tb_attention_rows_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
                                     const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
                                     int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
-                                    int mask_size, float scale, cudaStream_t stream) {
+                                    int mask_size, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
     if (rows == 0) return 0;
     if (!tb_attention_prompt_mma_supported(dim, vdim)) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || heads / kv_heads > 16 || page_size < 1) return TB_ERR_BAD_SIZE;
+    if (keys_per_value < 1 || kv_heads % keys_per_value != 0) return TB_ERR_BAD_SIZE;
     if (kv_heads > 65535) return TB_ERR_BAD_SIZE;
     if (mask_kind < MASK_CAUSAL || mask_kind > MASK_BLOCKS) return TB_ERR_BAD_SIZE;
     if (mask_kind != MASK_CAUSAL && mask_size < 1) return TB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 2 != 0) return TB_ERR_BAD_ALIGN;
 #define TB_ROWS(D, DV)                                                                                              \
     return launch_rows<D, DV>(q, q_stride, out, out_stride, cache, positions, seq_of_row, block_table, bt_stride,   \
-                              rows, heads, kv_heads, page_size, mask_kind, mask_size, scale, stream)
+                              rows, heads, kv_heads, page_size, mask_kind, mask_size, scale, keys_per_value, out_f32, stream)
     if (dim == 64 && vdim == 48) TB_ROWS(64, 48);
     if (dim == 64 && vdim == 64) TB_ROWS(64, 64);
     if (dim == 64 && vdim == 128) TB_ROWS(64, 128);

@@ -11,24 +11,48 @@
 // so that only non-negative powers of the decay appear (taken in 64-bit, once a block).  A step of single rows is
 // the chunk c = 1.  The order of the sums depends on where a step's rows start, so cutting a prompt differently moves
 // the result by rounding only.  q, k, v, the scores and the state are 32-bit inside the kernel whatever the run dtype.
+//
+// A step with long prompt portions takes three launches instead, so that the chunks of a sequence run side by side:
+// a tile is one chunk of one sequence (which block takes which follows from row_start alone);
+//   1. every tile's own sum  U = sum_s a^(c-1-s) k_s v_s^T                       (a block a tile, head and slice)
+//   2. per sequence, head and slice, the tiles in order:  S_0 = state,  S_(i+1) = a^(c_i) S_i + U_i ; every S_i is kept
+//      where U_i was, the last one goes back to the state slot
+//   3. every tile's outputs from its S_i and its own rows, as above.
 #include "common.cuh"
 
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kSlice = 32;          // value columns a block owns
+constexpr int kRows = 8;            // rows (or key dimensions) a warp carries in registers at a time
 
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 
+// The tile-th chunk of the step, counting every sequence's chunks in order: its sequence, first row and row count.
+__device__ __forceinline__ bool find_tile(const int* row_start, int num_seqs, int chunk, int tile, int& seq, int& r0, int& n) {
+    for (int s = 0; s < num_seqs; ++s) {
+        const int begin = row_start[s], rows = row_start[s + 1] - begin;
+        const int tiles = (rows + chunk - 1) / chunk;
+        if (tile < tiles) {
+            seq = s; r0 = begin + tile * chunk; n = min(chunk, rows - tile * chunk);
+            return true;
+        }
+        tile -= tiles;
+    }
+    return false;
+}
+
+// tile_state == nullptr: a block walks all rows of its sequence (blockIdx.x) from the state slot and renews the slot.
+// Otherwise blockIdx.x is a tile: its rows alone, from the state kept for it in tile_state; nothing is written back.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int k_off, int v_off,
                  const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ out,
                  const int* __restrict__ row_start, const int* __restrict__ state_slots, int heads, int dim, int vdim,
-                 int chunk) {
+                 int chunk, const float* __restrict__ tile_state, int num_seqs) {
     extern __shared__ __align__(16) float smem[];
     pdl_trigger();
-    const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kSlice;
+    const int head = blockIdx.y, col0 = blockIdx.z * kSlice;
     const int cols = min(kSlice, vdim - col0);
     const int dpad = dim + 1;
     float* qs = smem;                              // [chunk][dim + 1]
@@ -40,9 +64,18 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
     const float a = decay[head];
     for (int i = threadIdx.x; i <= chunk; i += kThreads) pw[i] = (float)pow((double)a, (double)i);
     pdl_wait();                                    // rows, state and the step's metadata come from kernels in front
-    const int first = row_start[seq], last = row_start[seq + 1];
+    int seq = blockIdx.x, first, last;
+    if (tile_state != nullptr) {
+        int n;
+        if (!find_tile(row_start, num_seqs, chunk, blockIdx.x, seq, first, n)) return;
+        last = first + n;
+    } else {
+        first = row_start[seq];
+        last = row_start[seq + 1];
+    }
     if (first >= last) return;
-    float* slot = state + ((int64_t)state_slots[seq] * heads + head) * dim * vdim;
+    float* slot = tile_state != nullptr ? const_cast<float*>(tile_state) + ((int64_t)blockIdx.x * heads + head) * dim * vdim
+                                        : state + ((int64_t)state_slots[seq] * heads + head) * dim * vdim;
     for (int e = threadIdx.x; e < dim * kSlice; e += kThreads) {
         const int i = e / kSlice, j = e % kSlice;
         S[e] = j < cols ? slot[(int64_t)i * vdim + col0 + j] : 0.0f;
@@ -76,22 +109,56 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
             A[t * chunk + s] = dot;
         }
         __syncthreads();
-        // outputs: warp `group` takes rows group, group + 8, ...; a lane a value column
-        for (int t = group; t < c; t += kThreads / 32) {
-            const float* qr = qs + t * dpad;
-            float from_state = 0.0f;
-            for (int i = 0; i < dim; ++i) from_state = fmaf(qr[i], S[i * kSlice + lane], from_state);
-            float inside = 0.0f;
-            for (int s = 0; s <= t; ++s) inside = fmaf(A[t * chunk + s], vs[s * kSlice + lane], inside);
-            if (lane < cols)
-                out[(int64_t)(row0 + t) * heads * vdim + (int64_t)head * vdim + col0 + lane] = fmaf(pw[t + 1], from_state, inside);
+        // outputs: a warp takes kRows neighbouring rows at a time, a lane a value column, so that a number of the state or
+        // of the values is read once for all of them
+        for (int t0 = group * kRows; t0 < c; t0 += (kThreads / 32) * kRows) {
+            const float* qr[kRows];
+            const float* ar[kRows];
+            float from_state[kRows], inside[kRows];
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                const int t = min(t0 + r, c - 1);
+                qr[r] = qs + t * dpad;
+                ar[r] = A + t * chunk;
+                from_state[r] = 0.0f;
+                inside[r] = 0.0f;
+            }
+            for (int i = 0; i < dim; ++i) {
+                const float sv = S[i * kSlice + lane];
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) from_state[r] = fmaf(qr[r][i], sv, from_state[r]);
+            }
+            const int reach = min(t0 + kRows, c);                 // (a row's scores behind itself are zeros)
+            for (int s = 0; s < reach; ++s) {
+                const float vv = vs[s * kSlice + lane];
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) inside[r] = fmaf(ar[r][s], vv, inside[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < kRows; ++r)
+                if (t0 + r < c && lane < cols)
+                    out[(int64_t)(row0 + t0 + r) * heads * vdim + (int64_t)head * vdim + col0 + lane] =
+                        fmaf(pw[t0 + r + 1], from_state[r], inside[r]);
         }
+        if (tile_state != nullptr) return;         // (a tile is one chunk; its state was made by the scan)
         __syncthreads();                           // every output of the chunk has read S
         // the state behind the chunk: warp `group` takes key dimensions group, group + 8, ...
-        for (int i = group; i < dim; i += kThreads / 32) {
-            float add = 0.0f;
-            for (int s = 0; s < c; ++s) add = fmaf(ks[s * dpad + i] * pw[c - 1 - s], vs[s * kSlice + lane], add);
-            S[i * kSlice + lane] = fmaf(pw[c], S[i * kSlice + lane], add);
+        for (int i0 = group * kRows; i0 < dim; i0 += (kThreads / 32) * kRows) {
+            float add[kRows];
+            int at[kRows];
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                add[r] = 0.0f;
+                at[r] = min(i0 + r, dim - 1);
+            }
+            for (int s = 0; s < c; ++s) {
+                const float vv = vs[s * kSlice + lane], power = pw[c - 1 - s];
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) add[r] = fmaf(ks[s * dpad + at[r]] * power, vv, add[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < kRows; ++r)
+                if (i0 + r < dim) S[(i0 + r) * kSlice + lane] = fmaf(pw[c], S[(i0 + r) * kSlice + lane], add[r]);
         }
     }
     __syncthreads();
@@ -101,17 +168,111 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
     }
 }
 
+// Launch 1 of the tiled form: U = sum_s a^(c-1-s) k_s v_s^T of one tile, head and slice of value columns, into
+// tile_state[tile][head] ([dim][vdim]).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+lightning_tile_sum_kernel(const T* __restrict__ proj, int64_t proj_stride, int k_off, int v_off,
+                          const float* __restrict__ decay, float* __restrict__ tile_state,
+                          const int* __restrict__ row_start, int num_seqs, int heads, int dim, int vdim, int chunk) {
+    extern __shared__ __align__(16) float smem[];
+    pdl_trigger();
+    const int head = blockIdx.y, col0 = blockIdx.z * kSlice;
+    const int cols = min(kSlice, vdim - col0);
+    const int dpad = dim + 1;
+    float* ks = smem;                              // [chunk][dim + 1]
+    float* vs = ks + chunk * dpad;                 // [chunk][kSlice]
+    float* pw = vs + chunk * kSlice;               // [chunk + 1]
+    const float a = decay[head];
+    for (int i = threadIdx.x; i <= chunk; i += kThreads) pw[i] = (float)pow((double)a, (double)i);
+    pdl_wait();
+    int seq, r0, c;
+    if (!find_tile(row_start, num_seqs, chunk, blockIdx.x, seq, r0, c)) return;
+    for (int e = threadIdx.x; e < c * dim; e += kThreads) {
+        const int t = e / dim, i = e % dim;
+        ks[t * dpad + i] = silu(Elem<T>::load(proj + (int64_t)(r0 + t) * proj_stride + k_off + (int64_t)head * dim + i));
+    }
+    for (int e = threadIdx.x; e < c * kSlice; e += kThreads) {
+        const int t = e / kSlice, j = e % kSlice;
+        vs[e] = j < cols ? silu(Elem<T>::load(proj + (int64_t)(r0 + t) * proj_stride + v_off + (int64_t)head * vdim + col0 + j))
+                         : 0.0f;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, group = threadIdx.x >> 5;
+    float* mine = tile_state + ((int64_t)blockIdx.x * heads + head) * dim * vdim;
+    for (int i0 = group * kRows; i0 < dim; i0 += (kThreads / 32) * kRows) {
+        float add[kRows];
+        int at[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            add[r] = 0.0f;
+            at[r] = min(i0 + r, dim - 1);
+        }
+        for (int s = 0; s < c; ++s) {
+            const float vv = vs[s * kSlice + lane], power = pw[c - 1 - s];
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) add[r] = fmaf(ks[s * dpad + at[r]] * power, vv, add[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+            if (i0 + r < dim && lane < cols) mine[(int64_t)(i0 + r) * vdim + col0 + lane] = add[r];
+    }
+}
+
+// Launch 2: per sequence and head, the tiles in order.  Every number of the state is a chain of its own.
+__global__ void __launch_bounds__(kThreads)
+lightning_scan_kernel(const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ tile_state,
+                      const int* __restrict__ row_start, const int* __restrict__ state_slots, int heads, int dim, int vdim,
+                      int chunk) {
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int rows = row_start[seq + 1] - row_start[seq];
+    if (rows <= 0) return;
+    int first_tile = 0;
+    for (int s = 0; s < seq; ++s) first_tile += (row_start[s + 1] - row_start[s] + chunk - 1) / chunk;
+    const int tiles = (rows + chunk - 1) / chunk;
+    const float a = decay[head];
+    const float whole = (float)pow((double)a, (double)chunk);
+    const float rest = (float)pow((double)a, (double)(rows - (tiles - 1) * chunk));
+    float* slot = state + ((int64_t)state_slots[seq] * heads + head) * dim * vdim;
+    const int64_t stride = (int64_t)heads * dim * vdim;
+    float* kept = tile_state + ((int64_t)first_tile * heads + head) * dim * vdim;
+    for (int e = blockIdx.z * kThreads + threadIdx.x; e < dim * vdim; e += gridDim.z * kThreads) {
+        float current = slot[e];
+        for (int i = 0; i < tiles; ++i) {
+            const float own = kept[i * stride + e];
+            kept[i * stride + e] = current;
+            current = fmaf(i + 1 < tiles ? whole : rest, current, own);
+        }
+        slot[e] = current;
+    }
+}
+
 size_t smem_for(int chunk, int dim) {
     return sizeof(float) * ((size_t)2 * chunk * (dim + 1) + (size_t)chunk * kSlice + (size_t)chunk * chunk +
                             (size_t)dim * kSlice + chunk + 1);
 }
 
-template <typename T>
-int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_off, const float* decay, float* state,
-           float* out, const int* row_start, const int* state_slots, int num_seqs, int heads, int dim, int vdim,
-           int max_new, cudaStream_t stream) {
+int chunk_for(int dim, int max_new) {
     int chunk = 64;
     while (chunk > 1 && (chunk / 2 >= max_new || smem_for(chunk, dim) > 200 * 1024)) chunk /= 2;
+    return chunk;
+}
+
+// Tiles of the three-launch form for a step of `rows` rows in `num_seqs` sequences (an upper bound that follows from
+// the counts alone), or 0 where a block walks its sequence: steps whose longest portion is shorter than four chunks.
+int tiles_for(int rows, int num_seqs, int dim, int max_new) {
+    const int chunk = chunk_for(dim, max_new);
+    if (max_new < 4 * chunk) return 0;
+    return (rows + chunk - 1) / chunk + num_seqs;
+}
+
+template <typename T>
+int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_off, const float* decay, float* state,
+           float* out, const int* row_start, const int* state_slots, int rows, int num_seqs, int heads, int dim, int vdim,
+           int max_new, float* tile_state, cudaStream_t stream) {
+    const int chunk = chunk_for(dim, max_new);
     const size_t smem = smem_for(chunk, dim);
     if (smem > 220 * 1024) return TB_ERR_BAD_SIZE;
     auto kernel = lightning_kernel<T>;
@@ -119,9 +280,32 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
-    const dim3 grid(num_seqs, heads, (vdim + kSlice - 1) / kSlice);
-    cudaError_t launched = tb_launch_pdl(kernel, grid, dim3(kThreads), smem, stream, (const T*)proj, proj_stride, q_off,
-                                         k_off, v_off, decay, state, out, row_start, state_slots, heads, dim, vdim, chunk);
+    const int slices = (vdim + kSlice - 1) / kSlice;
+    const int tiles = tiles_for(rows, num_seqs, dim, max_new);
+    if (tiles == 0) {
+        cudaError_t launched = tb_launch_pdl(kernel, dim3(num_seqs, heads, slices), dim3(kThreads), smem, stream,
+                                             (const T*)proj, proj_stride, q_off, k_off, v_off, decay, state, out, row_start,
+                                             state_slots, heads, dim, vdim, chunk, (const float*)nullptr, num_seqs);
+        return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+    }
+    if (tile_state == nullptr) return TB_ERR_BAD_SIZE;
+    auto sums = lightning_tile_sum_kernel<T>;
+    const size_t sums_smem = sizeof(float) * ((size_t)chunk * (dim + 1) + (size_t)chunk * kSlice + chunk + 1);
+    if (sums_smem > 40 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(sums, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sums_smem);
+        if (err != cudaSuccess) return (int)err;
+    }
+    cudaError_t launched = tb_launch_pdl(sums, dim3(tiles, heads, slices), dim3(kThreads), sums_smem, stream, (const T*)proj,
+                                         proj_stride, k_off, v_off, decay, tile_state, row_start, num_seqs, heads, dim,
+                                         vdim, chunk);
+    if (launched != cudaSuccess) return (int)launched;
+    const int parts = max(1, min(64, (dim * vdim + kThreads - 1) / kThreads));
+    launched = tb_launch_pdl(lightning_scan_kernel, dim3(num_seqs, heads, parts), dim3(kThreads), (size_t)0, stream, decay,
+                             state, tile_state, row_start, state_slots, heads, dim, vdim, chunk);
+    if (launched != cudaSuccess) return (int)launched;
+    launched = tb_launch_pdl(kernel, dim3(tiles, heads, slices), dim3(kThreads), smem, stream, (const T*)proj, proj_stride,
+                             q_off, k_off, v_off, decay, state, out, row_start, state_slots, heads, dim, vdim, chunk,
+                             (const float*)tile_state, num_seqs);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
@@ -129,18 +313,23 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
 
 // proj: [rows, ...] in `dtype`, row stride proj_stride (elements); q at column q_off ([heads, dim]), k at k_off ([heads, dim]),
 // v at v_off ([heads, vdim]), all before their activation.  decay: float32 [heads].  state: float32 [slots, heads, dim, vdim].
-// out: float32 [rows, heads * vdim].  max_new: the most rows any sequence brings (it sizes the chunk).
+// out: float32 [rows, heads * vdim].  max_new: the most rows any sequence brings (it sizes the chunk).  tile_state: float32
+// [tb_lightning_tiles(...), heads, dim, vdim] of scratch where that count is not 0.
+TB_EXPORT int tb_lightning_tiles(int rows, int num_seqs, int dim, int max_new) {
+    return (rows < 1 || num_seqs < 1 || dim < 1 || max_new < 1) ? 0 : tiles_for(rows, num_seqs, dim, max_new);
+}
+
 TB_EXPORT int tb_lightning(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_off, const float* decay,
-                           float* state, float* out, const int* row_start, const int* state_slots, int num_seqs,
-                           int heads, int dim, int vdim, int max_new, int dtype, cudaStream_t stream) {
-    if (num_seqs == 0) return 0;
+                           float* state, float* out, const int* row_start, const int* state_slots, int rows, int num_seqs,
+                           int heads, int dim, int vdim, int max_new, float* tile_state, int dtype, cudaStream_t stream) {
+    if (num_seqs == 0 || rows == 0) return 0;
     if (heads < 1 || heads > 65535 || dim < 1 || vdim < 1 || (vdim + kSlice - 1) / kSlice > 65535 || max_new < 1)
         return TB_ERR_BAD_SIZE;
     if (dtype == TB_F32)
-        return launch<float>(proj, proj_stride, q_off, k_off, v_off, decay, state, out, row_start, state_slots, num_seqs,
-                             heads, dim, vdim, max_new, stream);
+        return launch<float>(proj, proj_stride, q_off, k_off, v_off, decay, state, out, row_start, state_slots, rows,
+                             num_seqs, heads, dim, vdim, max_new, tile_state, stream);
     if (dtype == TB_BF16)
         return launch<__nv_bfloat16>(proj, proj_stride, q_off, k_off, v_off, decay, state, out, row_start, state_slots,
-                                     num_seqs, heads, dim, vdim, max_new, stream);
+                                     rows, num_seqs, heads, dim, vdim, max_new, tile_state, stream);
     return TB_ERR_BAD_DTYPE;
 }

@@ -850,40 +850,48 @@ def attention_prompt_mma_supported(dtype: torch.dtype, dim: int, vdim: int) -> b
 def attention_prompt_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
                          row_start: torch.Tensor, block_table: torch.Tensor, *, num_seqs: int, heads: int,
                          kv_heads: int, dim: int, vdim: int, page_size: int, mask_kind: int, mask_size: int,
-                         scale: float) -> torch.Tensor:
+                         scale: float, keys_per_value: int = 1) -> torch.Tensor:
     """:func:`attention_masked` (no sink, no gate) for bfloat16 prompt portions on the tensor cores: scores from
     exact bfloat16 products with 32-bit accumulation, 32-bit softmax, the 32-bit weights split in two bfloat16 halves
-    for the product with the values.  The rows of a sequence (``row_start``) stand at consecutive positions."""
+    for the product with the values.  The rows of a sequence (``row_start``) stand at consecutive positions.  ``out`` in
+    bfloat16 or float32 (the weighted sums unrounded); ``keys_per_value`` key heads in a row share a value head."""
     _cuda(q, out, cache, positions, row_start, block_table)
     rows = q.shape[0]
     _need(q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_prompt_mma q")
-    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype == q.dtype, "attention_prompt_mma out")
+    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype in (q.dtype, torch.float32),
+          "attention_prompt_mma out")
+    _need(keys_per_value >= 1 and kv_heads % keys_per_value == 0, "attention_prompt_mma keys_per_value")
     _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_prompt_mma cache")
     _need(row_start.dtype == torch.int32 and row_start.numel() >= num_seqs + 1, "attention_prompt_mma row_start")
     lib = load_library("attention_prompt_mma")
     _check(lib.tb_attention_prompt_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                        _ptr(positions), _ptr(row_start), _ptr(block_table), _i32(block_table.stride(0)),
                                        _i32(rows), _i32(num_seqs), _i32(heads), _i32(kv_heads), _i32(dim), _i32(vdim),
-                                       _i32(page_size), _i32(mask_kind), _i32(mask_size), _f32(scale), _stream()),
+                                       _i32(page_size), _i32(mask_kind), _i32(mask_size), _f32(scale),
+                                       _i32(keys_per_value), _i32(1 if out.dtype == torch.float32 else 0), _stream()),
            "attention_prompt_mma")
     return out
 
 
 def attention_rows_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
                        seq_of_row: torch.Tensor, block_table: torch.Tensor, *, heads: int, kv_heads: int, dim: int,
-                       vdim: int, page_size: int, mask_kind: int, mask_size: int, scale: float) -> torch.Tensor:
+                       vdim: int, page_size: int, mask_kind: int, mask_size: int, scale: float,
+                       keys_per_value: int = 1) -> torch.Tensor:
     """:func:`attention_prompt_mma` for steps of few rows at any positions: a block a (row, kv head), the kv head's
     query heads (at most 16) side by side in the tensor-core tile."""
     _cuda(q, out, cache, positions, seq_of_row, block_table)
     rows = q.shape[0]
     _need(q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_rows_mma q")
-    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype == q.dtype, "attention_rows_mma out")
+    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype in (q.dtype, torch.float32),
+          "attention_rows_mma out")
+    _need(keys_per_value >= 1 and kv_heads % keys_per_value == 0, "attention_rows_mma keys_per_value")
     _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_rows_mma cache")
     lib = load_library("attention_prompt_mma")
     _check(lib.tb_attention_rows_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                      _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
                                      _i32(rows), _i32(heads), _i32(kv_heads), _i32(dim), _i32(vdim), _i32(page_size),
-                                     _i32(mask_kind), _i32(mask_size), _f32(scale), _stream()), "attention_rows_mma")
+                                     _i32(mask_kind), _i32(mask_size), _f32(scale), _i32(keys_per_value),
+                                     _i32(1 if out.dtype == torch.float32 else 0), _stream()), "attention_rows_mma")
     return out
 
 
@@ -1214,9 +1222,16 @@ def lightning(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out:
     _need(decay.dtype == torch.float32 and decay.numel() == heads and decay.is_contiguous(), "lightning decay")
     _need(row_start.dtype == torch.int32 and state_slots.dtype == torch.int32, "lightning metadata must be int32")
     lib = load_library("lightning")
+    # long prompt portions: the chunks of a sequence run side by side and meet through this scratch
+    tiles = lib.tb_lightning_tiles(_i32(rows), _i32(num_seqs), _i32(dim), _i32(max(1, max_new)))
+    scratch = torch.empty((tiles, heads, dim, vdim), dtype=torch.float32, device=out.device) if tiles else None
     _check(lib.tb_lightning(_ptr(proj), _i64(proj.stride(0)), _i32(0), _i32(heads * dim), _i32(2 * heads * dim), _ptr(decay),
-                            _ptr(state), _ptr(out), _ptr(row_start), _ptr(state_slots), _i32(num_seqs), _i32(heads),
-                            _i32(dim), _i32(vdim), _i32(max(1, max_new)), _i32(_code(proj.dtype)), _stream()), "lightning")
+                            _ptr(state), _ptr(out), _ptr(row_start), _ptr(state_slots), _i32(rows), _i32(num_seqs),
+                            _i32(heads), _i32(dim), _i32(vdim), _i32(max(1, max_new)), _ptr(scratch),
+                            _i32(_code(proj.dtype)), _stream()), "lightning")
+    if tiles:
+        global launch_count
+        launch_count += 2          # (the tiles' sums and the scan in front of the outputs)
     return out
 
 

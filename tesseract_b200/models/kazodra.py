@@ -128,6 +128,15 @@ def kazodra_kernel_libraries(cfg: KazodraConfig, dtype: str):
         shared += ["differential", "attention_masked"]
     if KazodraLatentAttention in kinds:
         shared += ["latent_rope_cache", "attention_masked"]
+    if dtype != "float32":
+        import torch
+
+        from .. import kernels
+
+        if any(isinstance(layer.mixer, KazodraAttention)
+               and kernels.attention_prompt_mma_supported(torch.bfloat16, layer.mixer.dim, layer.mixer.vdim)
+               for layer in cfg.layers):
+            shared.append("attention_prompt_mma")     # (head sizes the tensor-core attention takes)
     shared = list(dict.fromkeys(shared))
     return shared + (["gemm_f32"] if dtype == "float32" else ["decode_linear", "skinny_tcgen05"])
 

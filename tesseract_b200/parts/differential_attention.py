@@ -13,7 +13,9 @@ Per row ``h`` (the mixer's input), with ``H`` heads, ``G`` kv heads, ``dim`` num
 
 To the attention kernel the maps are query heads: the query rows of the weight are reordered once, at load, to
 ``[kv head][map][head within the group]``, so that a run of ``H / G`` query heads reads key head ``2 g + map``, and
-both key heads of a group read value head ``g`` (``keys_per_value = 2``).  The kernel leaves its weighted sums in 32-bit;
+both key heads of a group read value head ``g`` (``keys_per_value = 2``).  In bfloat16, with head sizes they are built
+for, the tensor-core kernels take it (prompt portions in tiles, few rows a block each); the 32-bit row kernel otherwise.
+The kernel leaves its weighted sums in 32-bit;
 the subtraction, the norm and the gate are one kernel behind it, 32-bit up to the single rounding of its output.
 """
 
@@ -105,6 +107,11 @@ class DifferentialAttention(Mixer):
         """``(name, Linear, epilogue)`` of the mixer's matrix products, for the printed kernel plan."""
         return [("q/k/v/gate", self.in_proj, plan.BF16), ("o", self.o_proj, plan.F32 if self.stream_f32 else plan.BF16)]
 
+    def attention_choice(self, rows: int) -> str:
+        """The attention kernel of a step of ``rows`` rows (both maps of all heads in one launch)."""
+        return plan.masked_attention(self.runtime.dtype, rows, self.key_dim, self.value_dim,
+                                     heads_per_kv=self.num_heads // self.num_kv_heads)
+
     def cache_need(self):
         return PagedKeyValueNeed(num_kv_heads=2 * self.num_kv_heads, key_dim=self.key_dim, value_dim=self.value_dim,
                                  window=self.mask_size if self.mask_kind == "window" else None,
@@ -126,10 +133,17 @@ class DifferentialAttention(Mixer):
                                 q_heads=2 * H, key_heads=2 * G, value_heads=G, dim=self.key_dim, vdim=self.value_dim,
                                 rot_dims=self.rot_dims, page_size=cache.page_size)
         maps = torch.empty((rows, 2 * H * self.value_dim), dtype=torch.float32, device=proj.device)
-        kernels.attention_masked(q, None, maps, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
-                                 heads=2 * H, kv_heads=2 * G, dim=self.key_dim, vdim=self.value_dim,
-                                 page_size=cache.page_size, mask_kind=_MASKS[self.mask_kind], mask_size=self.mask_size,
-                                 sink=False, scale=self.scale, keys_per_value=2)
+        choice = self.attention_choice(rows)
+        common = dict(heads=2 * H, kv_heads=2 * G, dim=self.key_dim, vdim=self.value_dim, page_size=cache.page_size,
+                      mask_kind=_MASKS[self.mask_kind], mask_size=self.mask_size, scale=self.scale, keys_per_value=2)
+        if choice == "attention_rows_mma":
+            kernels.attention_rows_mma(q, maps, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table, **common)
+        elif choice == "attention_prompt_mma":
+            kernels.attention_prompt_mma(q, maps, cache.storage, ctx.positions, ctx.row_start, group.block_table,
+                                         num_seqs=ctx.num_seqs, **common)
+        else:
+            kernels.attention_masked(q, None, maps, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
+                                     sink=False, **common)
         out = torch.empty((rows, H * self.value_dim), dtype=proj.dtype, device=proj.device)
         kernels.differential_combine(maps, proj[:, self.gate_offset:] if self.gated else None, out, heads=H, kv_heads=G,
                                      vdim=self.value_dim, lam=self.lam, post=self.post_scale, eps=self.eps)

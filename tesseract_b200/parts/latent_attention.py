@@ -98,6 +98,10 @@ class LatentAttention(Mixer):
         return [("q", self.q_proj, plan.BF16), ("down", self.down_proj, plan.F32),
                 ("o", self.o_proj, plan.F32 if self.stream_f32 else plan.BF16)]
 
+    def attention_choice(self, rows: int) -> str:
+        """The attention kernel of a step of ``rows`` rows: one key head as wide as the cached entry."""
+        return "attention_masked"
+
     def cache_need(self):
         return PagedVectorNeed(width=self.entry, window=self.mask_size if self.mask_kind == "window" else None)
 

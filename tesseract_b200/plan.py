@@ -311,7 +311,9 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                 lines.append(f"    mixer    '{mixer.kind}' (its own kernels between the products)")
                 for name, linear, epilogue in mixer.products():
                     lines.append(f"      {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
-                if hasattr(mixer, "key_dim") and hasattr(mixer, "value_dim") and not hasattr(mixer, "taps"):
+                if hasattr(mixer, "attention_choice"):
+                    lines.append(f"      attend     {mixer.attention_choice(rows)}")
+                elif hasattr(mixer, "num_kv_heads") and hasattr(mixer, "value_dim") and not hasattr(mixer, "taps"):
                     per = mixer.num_heads // mixer.num_kv_heads
                     lines.append(f"      attend     {masked_attention(dtype, rows, mixer.key_dim, mixer.value_dim, heads_per_kv=per)}")
             else:

@@ -119,7 +119,8 @@ def latent_attention(h, t: Mapping[str, torch.Tensor], m: Mapping, eps: float, p
     q = rounded(h @ t["q"].T, round_to).view(T, H, d + dr)
     down = h @ t["dkv"].T
     latent = rounded(unit_rms(down[:, :rank], eps) * t["dkv.norm"], round_to)
-    frequencies = pair_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
+    rot = m.get("rot")
+    frequencies = pair_frequencies(rot["dims"], rot["base"], rot.get("scaling")) if rot else []
     shared = rounded(rotate_pairs(down[:, None, rank:], positions, frequencies), round_to)       # [T, 1, dr]
     q_rot = rounded(rotate_pairs(q[..., d:], positions, frequencies), round_to)
     k_plain = rounded(latent @ t["uk"].T, round_to).view(T, H, d)
@@ -169,8 +170,9 @@ def differential_attention(h, t: Mapping[str, torch.Tensor], m: Mapping, eps: fl
     group = H // G
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
-    first = softmax_attention(q[:, :, 0], k[:, :, 0], v, m["scale"], None)
-    second = softmax_attention(q[:, :, 1], k[:, :, 1], v, m["scale"], None)
+    window = (m.get("mask") or {}).get("size")
+    first = softmax_attention(q[:, :, 0], k[:, :, 0], v, m["scale"], window)
+    second = softmax_attention(q[:, :, 1], k[:, :, 1], v, m["scale"], window)
     out = unit_rms(first - differential_lambda(t, diff) * second, eps) * (1.0 - diff)
     gated = out.reshape(T, H * dv) * torch.sigmoid(rounded(h @ t["g"].T, round_to))
     return rounded(gated, round_to) @ t["o"].T
