@@ -1160,6 +1160,19 @@ def kazodra_kernels(size, pk):
 
         timed(f"attention_masked (latent, window {window})/{label}", latent_attend,
               rows * LH * (entry + rank) * 2 + latent_read, flops=window_keys * LH * 2 * (entry + rank))
+
+        def latent_attend_mma(k):
+            q_full = torch.randn(rows, LH * entry, device=dev).bfloat16()
+            mixed = torch.empty(rows, LH * rank, dtype=torch.bfloat16, device=dev)
+            cache = torch.randn(seqs * pages_per_seq + 1, page * entry, device=dev).bfloat16()
+            return lambda: kernels.attention_latent_mma(q_full, mixed, cache, positions, seq_of_row, table, heads=LH,
+                                                        dim=entry, vdim=rank, page_size=page,
+                                                        mask_kind=kernels.MASK_WINDOW, mask_size=window,
+                                                        scale=(ld + rot) ** -0.5)
+
+        if kernels.attention_latent_mma_supported(torch.bfloat16, entry, rank):
+            timed(f"attention_latent_mma (window {window})/{label}", latent_attend_mma,
+                  rows * LH * (entry + rank) * 2 + latent_read, flops=window_keys * LH * 2 * (entry + rank), tensor=True)
     return out
 
 

@@ -63,6 +63,7 @@ SOURCES: Dict[str, List[str]] = {
     "lightning": [],
     "differential": [],
     "latent_rope_cache": [],
+    "attention_latent_mma": [],
 }
 
 

@@ -111,7 +111,16 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
         __syncthreads();
         // outputs: a warp takes kRows neighbouring rows at a time, a lane a value column, so that a number of the state or
         // of the values is read once for all of them
-        for (int t0 = group * kRows; t0 < c; t0 += (kThreads / 32) * kRows) {
+        for (int t = group; c < kRows && t < c; t += kThreads / 32) {       // few rows (decoded ones): a warp a row
+            const float* qr = qs + t * dpad;
+            float from_state = 0.0f;
+            for (int i = 0; i < dim; ++i) from_state = fmaf(qr[i], S[i * kSlice + lane], from_state);
+            float inside = 0.0f;
+            for (int s = 0; s <= t; ++s) inside = fmaf(A[t * chunk + s], vs[s * kSlice + lane], inside);
+            if (lane < cols)
+                out[(int64_t)(row0 + t) * heads * vdim + (int64_t)head * vdim + col0 + lane] = fmaf(pw[t + 1], from_state, inside);
+        }
+        for (int t0 = group * kRows; c >= kRows && t0 < c; t0 += (kThreads / 32) * kRows) {
             const float* qr[kRows];
             const float* ar[kRows];
             float from_state[kRows], inside[kRows];

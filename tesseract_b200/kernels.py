@@ -1313,3 +1313,29 @@ def latent_rope_cache(down: torch.Tensor, q: torch.Tensor, q_full: torch.Tensor,
                                     _ptr(block_table), _i32(block_table.stride(0)), _ptr(inv_freq), _i32(rows), _i32(heads),
                                     _i32(dim), _i32(rank), _i32(rot_width), _i32(rot_dims), _i32(page_size), _f32(eps),
                                     _i32(_code(q.dtype)), _stream()), "latent_rope_cache")
+
+
+def attention_latent_mma_supported(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core attention over cached latent vectors takes these sizes (bfloat16 only; the sizes it is
+    instantiated for, as ``tb_attention_latent_mma_supported`` of the library says too: asked here without building it)."""
+    return dtype == torch.bfloat16 and (dim, vdim) in ((576, 512), (288, 256), (160, 128))
+
+
+def attention_latent_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                         seq_of_row: torch.Tensor, block_table: torch.Tensor, *, heads: int, dim: int, vdim: int,
+                         page_size: int, mask_kind: int, mask_size: int, scale: float) -> torch.Tensor:
+    """:func:`attention_masked` with ``kv_heads = 1`` and ``keys_per_value = 0`` (pages of ``[page_size, dim]`` vectors
+    whose first ``vdim`` numbers are the value) on the tensor cores, for bfloat16: a block a row and sixteen query heads;
+    exact bfloat16 products with 32-bit accumulation for the scores, 32-bit softmax, the weights as two bfloat16 halves."""
+    _cuda(q, out, cache, positions, seq_of_row, block_table)
+    rows = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_latent_mma q")
+    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype == q.dtype, "attention_latent_mma out")
+    _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_latent_mma cache")
+    _need(mask_kind in (MASK_CAUSAL, MASK_WINDOW), "attention_latent_mma mask")
+    lib = load_library("attention_latent_mma")
+    _check(lib.tb_attention_latent_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
+                                       _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
+                                       _i32(rows), _i32(heads), _i32(dim), _i32(vdim), _i32(page_size), _i32(mask_kind),
+                                       _i32(mask_size), _f32(scale), _stream()), "attention_latent_mma")
+    return out

@@ -137,6 +137,10 @@ def kazodra_kernel_libraries(cfg: KazodraConfig, dtype: str):
                and kernels.attention_prompt_mma_supported(torch.bfloat16, layer.mixer.dim, layer.mixer.vdim)
                for layer in cfg.layers):
             shared.append("attention_prompt_mma")     # (head sizes the tensor-core attention takes)
+        if any(isinstance(layer.mixer, KazodraLatentAttention)
+               and kernels.attention_latent_mma_supported(torch.bfloat16, layer.mixer.kv_rank + layer.mixer.rot_dim,
+                                                          layer.mixer.kv_rank) for layer in cfg.layers):
+            shared.append("attention_latent_mma")     # (latent sizes the tensor-core attention takes)
     shared = list(dict.fromkeys(shared))
     return shared + (["gemm_f32"] if dtype == "float32" else ["decode_linear", "skinny_tcgen05"])
 

@@ -13,8 +13,9 @@ Scores and outputs are taken in the latent space, so nothing per head is ever ke
 ``q_plain . (Uk_i c) = (Uk_i^T q_plain) . c`` and ``sum_j w_j Uv_i c_j = Uv_i (sum_j w_j c_j)``.  A batched product
 turns every head's plain query into ``rank`` numbers, the attention kernel runs with one key head of
 ``rank + rot_width`` numbers whose first ``rank`` are also its value, and a second batched product takes every head's
-output to ``vdim`` numbers; then the output projection.  Scores, softmax, weights and the weighted sums are 32-bit in
-the attention kernel; rotation, the latent's norm and the cache write are one kernel in front of it.
+output to ``vdim`` numbers; then the output projection.  In bfloat16, for the latent sizes it is built for, the
+attention kernel is the tensor-core one over cached vectors (a block a row and sixteen heads), else the 32-bit row
+kernel.  Scores, softmax, weights and the weighted sums are 32-bit in the attention kernel; rotation, the latent's norm and the cache write are one kernel in front of it.
 """
 
 from __future__ import annotations
@@ -100,7 +101,7 @@ class LatentAttention(Mixer):
 
     def attention_choice(self, rows: int) -> str:
         """The attention kernel of a step of ``rows`` rows: one key head as wide as the cached entry."""
-        return "attention_masked"
+        return plan.latent_attention(self.runtime.dtype, self.entry, self.rank)
 
     def cache_need(self):
         return PagedVectorNeed(width=self.entry, window=self.mask_size if self.mask_kind == "window" else None)
@@ -131,10 +132,15 @@ class LatentAttention(Mixer):
                                   group.block_table, self.inv_freq, heads=H, dim=d, rank=rank, rot_width=dr,
                                   rot_dims=self.rot_dims, page_size=cache.page_size, eps=self.eps)
         mixed = torch.empty((rows, H * rank), dtype=q.dtype, device=q.device)
-        kernels.attention_masked(q_full, None, mixed, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
-                                 heads=H, kv_heads=1, dim=self.entry, vdim=rank, page_size=cache.page_size,
-                                 mask_kind=_MASKS[self.mask_kind], mask_size=self.mask_size, sink=False, scale=self.scale,
-                                 keys_per_value=0)
+        if self.attention_choice(rows) == "attention_latent_mma":
+            kernels.attention_latent_mma(q_full, mixed, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
+                                         heads=H, dim=self.entry, vdim=rank, page_size=cache.page_size,
+                                         mask_kind=_MASKS[self.mask_kind], mask_size=self.mask_size, scale=self.scale)
+        else:
+            kernels.attention_masked(q_full, None, mixed, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
+                                     heads=H, kv_heads=1, dim=self.entry, vdim=rank, page_size=cache.page_size,
+                                     mask_kind=_MASKS[self.mask_kind], mask_size=self.mask_size, sink=False,
+                                     scale=self.scale, keys_per_value=0)
         out = torch.empty((rows, H * dv), dtype=q.dtype, device=q.device)
         self._per_head(mixed.view(rows, H, rank), self.up_v, out.view(rows, H, dv))
         return self.o_proj.forward(out, float32_out=self.stream_f32)

@@ -67,7 +67,7 @@ TINY_KAZODRA = {
     "e": {"architecture": "Kazodra", "width": 64, "vocab": 90, "norm": {"eps": 1e-6}, "token_side": {"dim": 4},
           "loop": {"start": 0, "stop": 2, "times": 2},
           "layers": [layer(differential(2, 1, 64, 128, 0.7, rot(64, 10000.0, (8.0, 1.0, 4.0, 128)), 0.125), 48),
-                     layer(latent(2, 64, 32, 128, 80, 100, rot(32, 100.0), 0.1), None),
+                     layer(latent(2, 64, 32, 128, 128, 100, rot(32, 100.0), 0.1), None),
                      layer(lightning(2, 64, 64, (0.95, 0.99)), 40),
                      layer(differential(4, 2, 128, 64, 0.4, rot(32, 100.0), 0.09), 32)]},
 }
@@ -96,7 +96,7 @@ def random_config(seed: int) -> dict:
         if kind == "latent":
             dim, rot_dim = r.choice([4, 8, 12, 24, 40, 64]), r.choice([0, 2, 8, 16, 32])
             mixer = latent(r.choice([1, 2, 3, 5, 8]), dim, rot_dim, r.choice([4, 8, 10, 24, 48, 64]),
-                           r.choice([6, 16, 20, 64, 96]), r.choice([None, 1, 3, 16, 17, 50, 64, 120, 500]),
+                           r.choice([6, 16, 20, 64, 96, 128, 128]), r.choice([None, 1, 3, 16, 17, 50, 64, 120, 500]),
                            rotation(rot_dim), r.choice([(dim + rot_dim) ** -0.5, 0.3, 0.07]))
         elif kind == "lightning":
             heads = r.choice([1, 2, 3, 4, 6])

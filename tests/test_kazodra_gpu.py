@@ -443,7 +443,8 @@ def test_two_maps_see_exactly_their_keys(dtype, heads, kv_heads, d, dv, window, 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,d,dr,dv,rank", [(3, 12, 8, 10, 20), (2, 16, 4, 24, 12), (1, 10, 6, 14, 9), (4, 8, 0, 4, 8),
-                                                (2, 64, 32, 128, 48), (2, 128, 64, 128, 192)])
+                                                (2, 64, 32, 128, 48), (2, 128, 64, 128, 192), (2, 16, 32, 24, 128),
+                                                (17, 32, 32, 16, 256), (3, 64, 64, 32, 512)])
 @pytest.mark.parametrize("window", [33, 16, 5, 1, None])
 def test_latent_attention_sees_exactly_its_keys(dtype, heads, d, dr, dv, rank, window):
     """Keys and values made from the cached latent and the shared rotated part: a marked row returns its marked key's
