@@ -25,8 +25,56 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kSlice = 32;          // value columns a block owns
 constexpr int kRows = 8;            // rows (or key dimensions) a warp carries in registers at a time
+static_assert(kRows == 8, "the vector forms below are written for eight");
 
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
+
+// Floats of a query or key row in shared memory.  Where dim is a multiple of four, rows start on 16 bytes and are read
+// four numbers at a time (the padding of four keeps a quarter-warp's rows on different banks); otherwise a number at a time.
+__host__ __device__ __forceinline__ int row_floats(int dim) { return dim % 4 == 0 ? dim + 4 : dim + 1; }
+
+// sum += a[0 .. n) . b[0 .. n), the products added in order
+__device__ __forceinline__ float dot_in_order(const float* a, const float* b, int n, bool vec, float sum) {
+    if (vec) {
+        for (int i = 0; i < n; i += 4) {
+            const float4 x = *reinterpret_cast<const float4*>(a + i), y = *reinterpret_cast<const float4*>(b + i);
+            sum = fmaf(x.x, y.x, sum); sum = fmaf(x.y, y.y, sum); sum = fmaf(x.z, y.z, sum); sum = fmaf(x.w, y.w, sum);
+        }
+    } else {
+        for (int i = 0; i < n; ++i) sum = fmaf(a[i], b[i], sum);
+    }
+    return sum;
+}
+
+// dst[t][0 .. n) = silu(src[t][0 .. valid)) and zeros behind, for c rows (src rows `stride` elements apart, dst rows
+// `dst_stride` floats): with PACKETS 16 bytes of the source at a time where its rows allow it, else an element at a time.
+template <typename T, bool PACKETS>
+__device__ __forceinline__ void load_silu_rows(float* dst, int dst_stride, const T* src, int64_t stride, int c, int n,
+                                               int valid) {
+    constexpr int N = Packet<T>::N;
+    if (PACKETS && n % N == 0 && valid % N == 0 && stride % N == 0 && (uintptr_t)src % 16 == 0) {
+        const int packets = n / N;
+        for (int e = threadIdx.x; e < c * packets; e += kThreads) {
+            const int t = e / packets, i = (e % packets) * N;
+            float v[N];
+            if (i < valid) {
+                Packet<T>::load(src + (int64_t)t * stride + i, v);
+#pragma unroll
+                for (int u = 0; u < N; ++u) v[u] = silu(v[u]);
+            } else {
+#pragma unroll
+                for (int u = 0; u < N; ++u) v[u] = 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < N; ++u) dst[t * dst_stride + i + u] = v[u];
+        }
+    } else {
+        for (int e = threadIdx.x; e < c * n; e += kThreads) {
+            const int t = e / n, i = e % n;
+            dst[t * dst_stride + i] = i < valid ? silu(Elem<T>::load(src + (int64_t)t * stride + i)) : 0.0f;
+        }
+    }
+}
 
 // The tile-th chunk of the step, counting every sequence's chunks in order: its sequence, first row and row count.
 __device__ __forceinline__ bool find_tile(const int* row_start, int num_seqs, int chunk, int tile, int& seq, int& r0, int& n) {
@@ -44,7 +92,10 @@ __device__ __forceinline__ bool find_tile(const int* row_start, int num_seqs, in
 
 // tile_state == nullptr: a block walks all rows of its sequence (blockIdx.x) from the state slot and renews the slot.
 // Otherwise blockIdx.x is a tile: its rows alone, from the state kept for it in tile_state; nothing is written back.
-template <typename T>
+// WIDE: chunks of kRows rows or more (prompt portions), a warp carrying kRows rows or key dimensions in registers;
+// otherwise (steps of few rows a sequence, decoded ones) a warp a row, which needs half the registers: twice the blocks
+// stream their states side by side.
+template <typename T, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
 lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int k_off, int v_off,
                  const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ out,
@@ -54,9 +105,10 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
     pdl_trigger();
     const int head = blockIdx.y, col0 = blockIdx.z * kSlice;
     const int cols = min(kSlice, vdim - col0);
-    const int dpad = dim + 1;
-    float* qs = smem;                              // [chunk][dim + 1]
-    float* ks = qs + chunk * dpad;                 // [chunk][dim + 1]
+    const int dpad = row_floats(dim);
+    const bool vec = dim % 4 == 0;
+    float* qs = smem;                              // [chunk][row_floats(dim)]
+    float* ks = qs + chunk * dpad;                 // [chunk][row_floats(dim)]
     float* vs = ks + chunk * dpad;                 // [chunk][kSlice]
     float* A = vs + chunk * kSlice;                // [chunk][chunk]
     float* S = A + chunk * chunk;                  // [dim][kSlice]
@@ -84,34 +136,24 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
     for (int row0 = first; row0 < last; row0 += chunk) {
         const int c = min(chunk, last - row0);
         __syncthreads();                           // the chunk before is done with qs, ks, vs, A (and S is written)
-        for (int e = threadIdx.x; e < c * dim; e += kThreads) {
-            const int t = e / dim, i = e % dim;
-            const T* p = proj + (int64_t)(row0 + t) * proj_stride + (int64_t)head * dim + i;
-            qs[t * dpad + i] = silu(Elem<T>::load(p + q_off));
-            ks[t * dpad + i] = silu(Elem<T>::load(p + k_off));
-        }
-        for (int e = threadIdx.x; e < c * kSlice; e += kThreads) {
-            const int t = e / kSlice, j = e % kSlice;
-            vs[e] = j < cols ? silu(Elem<T>::load(proj + (int64_t)(row0 + t) * proj_stride + v_off + (int64_t)head * vdim + col0 + j))
-                             : 0.0f;
-        }
+        const T* rows_at = proj + (int64_t)row0 * proj_stride;
+        load_silu_rows<T, WIDE>(qs, dpad, rows_at + q_off + (int64_t)head * dim, proj_stride, c, dim, dim);
+        load_silu_rows<T, WIDE>(ks, dpad, rows_at + k_off + (int64_t)head * dim, proj_stride, c, dim, dim);
+        load_silu_rows<T, WIDE>(vs, kSlice, rows_at + v_off + (int64_t)head * vdim + col0, proj_stride, c, kSlice, cols);
         __syncthreads();
         // scores of the chunk: thread e takes (t, s) with s fastest, so neighbouring lanes read neighbouring key rows
         for (int e = threadIdx.x; e < c * c; e += kThreads) {
             const int t = e / c, s = e % c;
             float dot = 0.0f;
             if (s <= t) {
-                const float* qr = qs + t * dpad;
-                const float* kr = ks + s * dpad;
-                for (int i = 0; i < dim; ++i) dot = fmaf(qr[i], kr[i], dot);
-                dot *= pw[t - s];
+                dot = dot_in_order(qs + t * dpad, ks + s * dpad, dim, vec, 0.0f) * pw[t - s];
             }
             A[t * chunk + s] = dot;
         }
         __syncthreads();
         // outputs: a warp takes kRows neighbouring rows at a time, a lane a value column, so that a number of the state or
         // of the values is read once for all of them
-        for (int t = group; c < kRows && t < c; t += kThreads / 32) {       // few rows (decoded ones): a warp a row
+        for (int t = group; (!WIDE || c < kRows) && t < c; t += kThreads / 32) {       // few rows: a warp a row
             const float* qr = qs + t * dpad;
             float from_state = 0.0f;
             for (int i = 0; i < dim; ++i) from_state = fmaf(qr[i], S[i * kSlice + lane], from_state);
@@ -120,7 +162,7 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
             if (lane < cols)
                 out[(int64_t)(row0 + t) * heads * vdim + (int64_t)head * vdim + col0 + lane] = fmaf(pw[t + 1], from_state, inside);
         }
-        for (int t0 = group * kRows; c >= kRows && t0 < c; t0 += (kThreads / 32) * kRows) {
+        for (int t0 = group * kRows; WIDE && c >= kRows && t0 < c; t0 += (kThreads / 32) * kRows) {
             const float* qr[kRows];
             const float* ar[kRows];
             float from_state[kRows], inside[kRows];
@@ -132,13 +174,37 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
                 from_state[r] = 0.0f;
                 inside[r] = 0.0f;
             }
-            for (int i = 0; i < dim; ++i) {
-                const float sv = S[i * kSlice + lane];
+            if (vec) {
+                for (int i = 0; i < dim; i += 4) {
+                    const float s0 = S[i * kSlice + lane], s1 = S[(i + 1) * kSlice + lane];
+                    const float s2 = S[(i + 2) * kSlice + lane], s3 = S[(i + 3) * kSlice + lane];
 #pragma unroll
-                for (int r = 0; r < kRows; ++r) from_state[r] = fmaf(qr[r][i], sv, from_state[r]);
+                    for (int r = 0; r < kRows; ++r) {
+                        const float4 qv = *reinterpret_cast<const float4*>(qr[r] + i);
+                        from_state[r] = fmaf(qv.x, s0, from_state[r]); from_state[r] = fmaf(qv.y, s1, from_state[r]);
+                        from_state[r] = fmaf(qv.z, s2, from_state[r]); from_state[r] = fmaf(qv.w, s3, from_state[r]);
+                    }
+                }
+            } else {
+                for (int i = 0; i < dim; ++i) {
+                    const float sv = S[i * kSlice + lane];
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r) from_state[r] = fmaf(qr[r][i], sv, from_state[r]);
+                }
             }
             const int reach = min(t0 + kRows, c);                 // (a row's scores behind itself are zeros)
-            for (int s = 0; s < reach; ++s) {
+            int s = 0;
+            for (; s + 4 <= reach; s += 4) {                      // (chunk is a multiple of four here: rows of A start on 16 bytes)
+                const float v0 = vs[s * kSlice + lane], v1 = vs[(s + 1) * kSlice + lane];
+                const float v2 = vs[(s + 2) * kSlice + lane], v3 = vs[(s + 3) * kSlice + lane];
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) {
+                    const float4 av = *reinterpret_cast<const float4*>(ar[r] + s);
+                    inside[r] = fmaf(av.x, v0, inside[r]); inside[r] = fmaf(av.y, v1, inside[r]);
+                    inside[r] = fmaf(av.z, v2, inside[r]); inside[r] = fmaf(av.w, v3, inside[r]);
+                }
+            }
+            for (; s < reach; ++s) {
                 const float vv = vs[s * kSlice + lane];
 #pragma unroll
                 for (int r = 0; r < kRows; ++r) inside[r] = fmaf(ar[r][s], vv, inside[r]);
@@ -151,8 +217,13 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
         }
         if (tile_state != nullptr) return;         // (a tile is one chunk; its state was made by the scan)
         __syncthreads();                           // every output of the chunk has read S
-        // the state behind the chunk: warp `group` takes key dimensions group, group + 8, ...
-        for (int i0 = group * kRows; i0 < dim; i0 += (kThreads / 32) * kRows) {
+        // the state behind the chunk: warp `group` takes key dimensions group, group + 8, ... (WIDE: kRows at a time)
+        for (int i = group; !WIDE && i < dim; i += kThreads / 32) {
+            float add = 0.0f;
+            for (int s = 0; s < c; ++s) add = fmaf(ks[s * dpad + i] * pw[c - 1 - s], vs[s * kSlice + lane], add);
+            S[i * kSlice + lane] = fmaf(pw[c], S[i * kSlice + lane], add);
+        }
+        for (int i0 = group * kRows; WIDE && i0 < dim; i0 += (kThreads / 32) * kRows) {
             float add[kRows];
             int at[kRows];
 #pragma unroll
@@ -160,10 +231,22 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
                 add[r] = 0.0f;
                 at[r] = min(i0 + r, dim - 1);
             }
-            for (int s = 0; s < c; ++s) {
-                const float vv = vs[s * kSlice + lane], power = pw[c - 1 - s];
+            if (vec && i0 + kRows <= dim) {
+                for (int s = 0; s < c; ++s) {
+                    const float vv = vs[s * kSlice + lane], power = pw[c - 1 - s];
+                    const float4 k0 = *reinterpret_cast<const float4*>(ks + s * dpad + i0);
+                    const float4 k1 = *reinterpret_cast<const float4*>(ks + s * dpad + i0 + 4);
+                    add[0] = fmaf(k0.x * power, vv, add[0]); add[1] = fmaf(k0.y * power, vv, add[1]);
+                    add[2] = fmaf(k0.z * power, vv, add[2]); add[3] = fmaf(k0.w * power, vv, add[3]);
+                    add[4] = fmaf(k1.x * power, vv, add[4]); add[5] = fmaf(k1.y * power, vv, add[5]);
+                    add[6] = fmaf(k1.z * power, vv, add[6]); add[7] = fmaf(k1.w * power, vv, add[7]);
+                }
+            } else {
+                for (int s = 0; s < c; ++s) {
+                    const float vv = vs[s * kSlice + lane], power = pw[c - 1 - s];
 #pragma unroll
-                for (int r = 0; r < kRows; ++r) add[r] = fmaf(ks[s * dpad + at[r]] * power, vv, add[r]);
+                    for (int r = 0; r < kRows; ++r) add[r] = fmaf(ks[s * dpad + at[r]] * power, vv, add[r]);
+                }
             }
 #pragma unroll
             for (int r = 0; r < kRows; ++r)
@@ -188,8 +271,9 @@ lightning_tile_sum_kernel(const T* __restrict__ proj, int64_t proj_stride, int k
     pdl_trigger();
     const int head = blockIdx.y, col0 = blockIdx.z * kSlice;
     const int cols = min(kSlice, vdim - col0);
-    const int dpad = dim + 1;
-    float* ks = smem;                              // [chunk][dim + 1]
+    const int dpad = row_floats(dim);
+    const bool vec = dim % 4 == 0;
+    float* ks = smem;                              // [chunk][row_floats(dim)]
     float* vs = ks + chunk * dpad;                 // [chunk][kSlice]
     float* pw = vs + chunk * kSlice;               // [chunk + 1]
     const float a = decay[head];
@@ -197,15 +281,9 @@ lightning_tile_sum_kernel(const T* __restrict__ proj, int64_t proj_stride, int k
     pdl_wait();
     int seq, r0, c;
     if (!find_tile(row_start, num_seqs, chunk, blockIdx.x, seq, r0, c)) return;
-    for (int e = threadIdx.x; e < c * dim; e += kThreads) {
-        const int t = e / dim, i = e % dim;
-        ks[t * dpad + i] = silu(Elem<T>::load(proj + (int64_t)(r0 + t) * proj_stride + k_off + (int64_t)head * dim + i));
-    }
-    for (int e = threadIdx.x; e < c * kSlice; e += kThreads) {
-        const int t = e / kSlice, j = e % kSlice;
-        vs[e] = j < cols ? silu(Elem<T>::load(proj + (int64_t)(r0 + t) * proj_stride + v_off + (int64_t)head * vdim + col0 + j))
-                         : 0.0f;
-    }
+    const T* rows_at = proj + (int64_t)r0 * proj_stride;
+    load_silu_rows<T, true>(ks, dpad, rows_at + k_off + (int64_t)head * dim, proj_stride, c, dim, dim);
+    load_silu_rows<T, true>(vs, kSlice, rows_at + v_off + (int64_t)head * vdim + col0, proj_stride, c, kSlice, cols);
     __syncthreads();
     const int lane = threadIdx.x & 31, group = threadIdx.x >> 5;
     float* mine = tile_state + ((int64_t)blockIdx.x * heads + head) * dim * vdim;
@@ -217,10 +295,22 @@ lightning_tile_sum_kernel(const T* __restrict__ proj, int64_t proj_stride, int k
             add[r] = 0.0f;
             at[r] = min(i0 + r, dim - 1);
         }
-        for (int s = 0; s < c; ++s) {
-            const float vv = vs[s * kSlice + lane], power = pw[c - 1 - s];
+        if (vec && i0 + kRows <= dim) {
+            for (int s = 0; s < c; ++s) {
+                const float vv = vs[s * kSlice + lane], power = pw[c - 1 - s];
+                const float4 k0 = *reinterpret_cast<const float4*>(ks + s * dpad + i0);
+                const float4 k1 = *reinterpret_cast<const float4*>(ks + s * dpad + i0 + 4);
+                add[0] = fmaf(k0.x * power, vv, add[0]); add[1] = fmaf(k0.y * power, vv, add[1]);
+                add[2] = fmaf(k0.z * power, vv, add[2]); add[3] = fmaf(k0.w * power, vv, add[3]);
+                add[4] = fmaf(k1.x * power, vv, add[4]); add[5] = fmaf(k1.y * power, vv, add[5]);
+                add[6] = fmaf(k1.z * power, vv, add[6]); add[7] = fmaf(k1.w * power, vv, add[7]);
+            }
+        } else {
+            for (int s = 0; s < c; ++s) {
+                const float vv = vs[s * kSlice + lane], power = pw[c - 1 - s];
 #pragma unroll
-            for (int r = 0; r < kRows; ++r) add[r] = fmaf(ks[s * dpad + at[r]] * power, vv, add[r]);
+                for (int r = 0; r < kRows; ++r) add[r] = fmaf(ks[s * dpad + at[r]] * power, vv, add[r]);
+            }
         }
 #pragma unroll
         for (int r = 0; r < kRows; ++r)
@@ -259,7 +349,7 @@ lightning_scan_kernel(const float* __restrict__ decay, float* __restrict__ state
 }
 
 size_t smem_for(int chunk, int dim) {
-    return sizeof(float) * ((size_t)2 * chunk * (dim + 1) + (size_t)chunk * kSlice + (size_t)chunk * chunk +
+    return sizeof(float) * ((size_t)2 * chunk * row_floats(dim) + (size_t)chunk * kSlice + (size_t)chunk * chunk +
                             (size_t)dim * kSlice + chunk + 1);
 }
 
@@ -284,7 +374,7 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
     const int chunk = chunk_for(dim, max_new);
     const size_t smem = smem_for(chunk, dim);
     if (smem > 220 * 1024) return TB_ERR_BAD_SIZE;
-    auto kernel = lightning_kernel<T>;
+    auto kernel = chunk >= kRows ? lightning_kernel<T, true> : lightning_kernel<T, false>;
     if (smem > 40 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
@@ -299,7 +389,7 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
     }
     if (tile_state == nullptr) return TB_ERR_BAD_SIZE;
     auto sums = lightning_tile_sum_kernel<T>;
-    const size_t sums_smem = sizeof(float) * ((size_t)chunk * (dim + 1) + (size_t)chunk * kSlice + chunk + 1);
+    const size_t sums_smem = sizeof(float) * ((size_t)chunk * row_floats(dim) + (size_t)chunk * kSlice + chunk + 1);
     if (sums_smem > 40 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(sums, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sums_smem);
         if (err != cudaSuccess) return (int)err;

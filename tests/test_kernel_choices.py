@@ -142,3 +142,11 @@ def test_masked_attention_goes_to_the_tensor_cores_for_many_bfloat16_rows_of_siz
     assert plan.masked_attention(torch.bfloat16, 2048, 40, 64) == "attention_masked"         # a head size it is not built for
     assert plan.masked_attention(torch.bfloat16, 2048, 64, 64, sink=True) == "attention_masked"
     assert plan.masked_attention(torch.bfloat16, 2048, 64, 64, gated=True) == "attention_masked"
+
+
+def test_attention_over_cached_latents_goes_to_the_tensor_cores_for_the_sizes_it_is_built_for():
+    assert plan.latent_attention(torch.bfloat16, 576, 512) == "attention_latent_mma"
+    assert plan.latent_attention(torch.bfloat16, 288, 256) == "attention_latent_mma"
+    assert plan.latent_attention(torch.bfloat16, 160, 128) == "attention_latent_mma"
+    assert plan.latent_attention(torch.bfloat16, 128, 96) == "attention_masked"        # a size it is not built for
+    assert plan.latent_attention(torch.float32, 576, 512) == "attention_masked"        # the true 32-bit path
