@@ -11,6 +11,7 @@
 // so that only non-negative powers of the decay appear (taken in 64-bit, once a block).  A step of single rows is
 // the chunk c = 1.  The order of the sums depends on where a step's rows start, so cutting a prompt differently moves
 // the result by rounding only.  q, k, v, the scores and the state are 32-bit inside the kernel whatever the run dtype.
+// A step of single rows has a kernel of its own that keeps no copy of the state in shared memory.
 //
 // A step with long prompt portions takes three launches instead, so that the chunks of a sequence run side by side:
 // a tile is one chunk of one sequence (which block takes which follows from row_start alone);
@@ -260,6 +261,58 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
     }
 }
 
+// A step of single rows (decoded ones): every number of the state is read once, renewed and written once, straight
+// from and to the slot; a lane a value column, a warp every eighth key dimension, the warps' parts of S^T q summed in
+// warp order.  o = a (S^T q) + (q . k) v,  S' = a S + k v^T.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+lightning_step_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int k_off, int v_off,
+                      const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ out,
+                      const int* __restrict__ row_start, const int* __restrict__ state_slots, int heads, int dim, int vdim) {
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                              // [dim]
+    float* ks = qs + dim;                          // [dim]
+    float* parts = ks + dim;                       // [warps][kSlice], then the dot product q . k
+    pdl_trigger();
+    const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kSlice;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kWarps = kThreads / 32;
+    const float a = decay[head];
+    pdl_wait();
+    const int row = row_start[seq];
+    if (row >= row_start[seq + 1]) return;
+    const T* p = proj + (int64_t)row * proj_stride + (int64_t)head * dim;
+    for (int i = threadIdx.x; i < dim; i += kThreads) {
+        qs[i] = silu(Elem<T>::load(p + q_off + i));
+        ks[i] = silu(Elem<T>::load(p + k_off + i));
+    }
+    const bool there = col0 + lane < vdim;
+    const float v = there ? silu(Elem<T>::load(proj + (int64_t)row * proj_stride + v_off + (int64_t)head * vdim + col0 + lane)) : 0.0f;
+    __syncthreads();
+    float* slot = state + ((int64_t)state_slots[seq] * heads + head) * dim * vdim + col0 + lane;
+    float from_state = 0.0f;
+    if (there)
+        for (int i = warp; i < dim; i += kWarps) {
+            const float old = slot[(int64_t)i * vdim];
+            from_state = fmaf(qs[i], old, from_state);
+            slot[(int64_t)i * vdim] = fmaf(a, old, ks[i] * v);
+        }
+    parts[warp * kSlice + lane] = from_state;
+    if (warp == 0) {
+        float dot = 0.0f;
+        for (int i = lane; i < dim; i += 32) dot = fmaf(qs[i], ks[i], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) parts[kWarps * kSlice] = dot;
+    }
+    __syncthreads();
+    if (warp == 0 && there) {
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) total += parts[w * kSlice + lane];
+        out[(int64_t)row * heads * vdim + (int64_t)head * vdim + col0 + lane] = fmaf(a, total, parts[kWarps * kSlice] * v);
+    }
+}
+
 // Launch 1 of the tiled form: U = sum_s a^(c-1-s) k_s v_s^T of one tile, head and slice of value columns, into
 // tile_state[tile][head] ([dim][vdim]).
 template <typename T>
@@ -380,6 +433,14 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
         if (err != cudaSuccess) return (int)err;
     }
     const int slices = (vdim + kSlice - 1) / kSlice;
+    if (max_new == 1) {                                           // single rows: the state straight from and to its slot
+        const size_t step_smem = sizeof(float) * ((size_t)2 * dim + (kThreads / 32) * kSlice + 1);
+        if (step_smem > 40 * 1024) return TB_ERR_BAD_SIZE;
+        cudaError_t launched = tb_launch_pdl(lightning_step_kernel<T>, dim3(num_seqs, heads, slices), dim3(kThreads),
+                                             step_smem, stream, (const T*)proj, proj_stride, q_off, k_off, v_off, decay,
+                                             state, out, row_start, state_slots, heads, dim, vdim);
+        return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+    }
     const int tiles = tiles_for(rows, num_seqs, dim, max_new);
     if (tiles == 0) {
         cudaError_t launched = tb_launch_pdl(kernel, dim3(num_seqs, heads, slices), dim3(kThreads), smem, stream,
