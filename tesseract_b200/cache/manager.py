@@ -78,11 +78,12 @@ class CacheManager:
         for group in self.groups:
             need = group.need
             if isinstance(need, PagedNeed):
-                group.pool = PagePool(num_pages, first_page=1)
+                pages = need.pool_pages(num_pages, max_requests)     # (fewer where an entry serves several positions)
+                group.pool = PagePool(pages, first_page=1)
                 group.tables = np.zeros((max_requests, 8), dtype=np.int32)
                 if allocate_storage:      # the need says what a page looks like; page 0 is the scratch page
                     group.storage = torch.zeros(
-                        (len(group.entries), num_pages + 1, *need.page_shape(page_size)),
+                        (len(group.entries), pages + 1, *need.page_shape(page_size)),
                         dtype=need.dtype or dtype, device=device)
             elif isinstance(need, StateNeed):
                 if allocate_storage:
@@ -112,7 +113,7 @@ class CacheManager:
     # ------------------------------------------------------------------ sizes
     def pages_for(self, group: _Group, tokens: int) -> int:
         """Peak pages a request of ``tokens`` tokens holds in ``group`` at any one time."""
-        total = -(-tokens // self.page_size)
+        total = -(-group.need.entries_for(tokens) // self.page_size)
         span = group.need.live_span()
         if span is not None:
             live = -(-(span + self.max_step_tokens) // self.page_size) + 1
@@ -174,10 +175,10 @@ class CacheManager:
     def extend(self, request: Hashable, new_tokens: int) -> None:
         """Make sure pages exist for positions ``[length, length + new_tokens)`` in every paged group."""
         state = self._requests[request]
-        last = (state.length + new_tokens - 1) // self.page_size
         for index, g in enumerate(self.groups):
             if g.pool is None:
                 continue
+            last = (g.need.entries_for(state.length + new_tokens) - 1) // self.page_size
             held = state.pages[index]
             if g.tables.shape[1] <= last:
                 columns = max(last + 1, 2 * g.tables.shape[1])

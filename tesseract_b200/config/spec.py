@@ -63,11 +63,14 @@ class LayerSpec:
     norms_items: Tuple[Tuple[str, PartSpec], ...]
     # a term that the layer adds behind its sublayers from the step's tokens (a block kind that takes one), or None
     token_input: Optional[PartSpec] = None
+    # what weights every sublayer's result on its way into the stream (a block kind that takes one), or None
+    residual_gates: Optional[PartSpec] = None
 
     @classmethod
     def make(cls, block: str, mixer: PartSpec, feed_forward: Optional[PartSpec],
-             norms: Mapping[str, PartSpec], token_input: Optional[PartSpec] = None) -> "LayerSpec":
-        return cls(block, mixer, feed_forward, tuple(sorted(norms.items())), token_input)
+             norms: Mapping[str, PartSpec], token_input: Optional[PartSpec] = None,
+             residual_gates: Optional[PartSpec] = None) -> "LayerSpec":
+        return cls(block, mixer, feed_forward, tuple(sorted(norms.items())), token_input, residual_gates)
 
     @property
     def norms(self) -> Dict[str, PartSpec]:

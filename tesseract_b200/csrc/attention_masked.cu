@@ -1,11 +1,16 @@
 // Paged attention with 32-bit scores and weights, for mixers whose keys and values have widths of their own and
 // whose mask, denominator and output are parameters:
 //
-//   mask     causal (every key up to the row's position), a sliding window of `mask_size` keys, or blocks: the
+//   mask     causal (every key up to the row's position), a sliding window of `mask_size` keys, blocks (the
 //            positions of a sequence are cut into consecutive blocks of `mask_size`, counted from position 0, and
-//            a row sees the keys of its own block up to its own position;
-//   sink     the softmax denominator has one more entry of score 0 that carries no value:
-//            w_j = exp(s_j) / (1 + sum_j exp(s_j));
+//            a row sees the keys of its own block up to its own position), or a window with pooled blocks: beside
+//            the window's keys a row at position p sees one averaged key and value for every block of `pool`
+//            positions that lies wholly in front of the window (block b if b * pool + pool - 1 <= p - mask_size);
+//            the averages live in pages of their own (entry b of the request's pooled pages, same page layout), are
+//            walked first, and share the softmax with the window's keys;
+//   sink     the softmax denominator has one more entry that carries no value, of score 0
+//            (w_j = exp(s_j) / (1 + sum_j exp(s_j))) or, with `sinks`, of a learned score per query head;
+//   softcap  with softcap > 0 a score s becomes softcap * tanh(s / softcap) (the sink's score is not touched);
 //   gate     the output is multiplied, element by element, by sigmoid(gate[row, head, :]).
 //
 // One warp per (query row, query head).  Keys are walked from the first visible one in blocks of 32, a lane a key:
@@ -31,7 +36,35 @@
 namespace {
 
 constexpr int kWarps = 4;
-enum MaskKind : int { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_BLOCKS = 2 };
+enum MaskKind : int { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_BLOCKS = 2, MASK_WINDOW_POOLED = 3 };
+
+// What only some mixers use: a learned sink score per query head (null: none, or the fixed 0 of `sink`), a cap on the
+// scores (0: none), and the pooled blocks of MASK_WINDOW_POOLED (their pages, the requests' tables of those pages and
+// the tokens a block holds).
+struct MaskExtras {
+    const float* sinks;
+    float softcap;
+    const void* pool_cache;
+    const int* pool_table;
+    int pool_bt_stride, pool;
+};
+
+__device__ __forceinline__ float capped(float s, float softcap) {
+    return softcap > 0.0f ? softcap * tanhf(s / softcap) : s;
+}
+
+// The keys of a row in the order they are walked: `pooled` averaged blocks, then the positions first_key .. pos.
+struct Reach {
+    int first_key, pooled, total;
+    __device__ Reach(int pos, int mask_kind, int mask_size, int pool) {
+        first_key = 0;
+        pooled = 0;
+        if (mask_kind == MASK_WINDOW || mask_kind == MASK_WINDOW_POOLED) first_key = pos - mask_size + 1 > 0 ? pos - mask_size + 1 : 0;
+        else if (mask_kind == MASK_BLOCKS) first_key = (pos / mask_size) * mask_size;
+        if (mask_kind == MASK_WINDOW_POOLED) pooled = first_key / pool;       // blocks that end in front of the window
+        total = pooled + pos - first_key + 1;
+    }
+};
 
 // Where a page keeps what.  keys_per_value >= 1: [kv_heads][page][dim] keys, then [kv_heads / keys_per_value][page][vdim]
 // values, key head g reading value head g / keys_per_value (1: the usual layout; 2: two score maps over one set of
@@ -61,7 +94,7 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
                         const int* __restrict__ positions, const int* __restrict__ seq_of_row,
                         const int* __restrict__ block_table, int bt_stride, int heads, int kv_heads, int dim, int vdim,
                         int page_size, int mask_kind, int mask_size, int sink, float scale, int keys_per_value,
-                        int out_f32) {
+                        int out_f32, MaskExtras extras) {
     extern __shared__ float q_smem[];                 // kWarps * dim
     pdl_trigger();
     pdl_wait();                                       // queries, pages and the step's metadata come from kernels in front
@@ -72,9 +105,7 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
     const int kv_head = head / (heads / kv_heads);
     const int pos = positions[row];
     const int seq = seq_of_row[row];
-    int first_key = 0;
-    if (mask_kind == MASK_WINDOW) first_key = pos - mask_size + 1 > 0 ? pos - mask_size + 1 : 0;
-    else if (mask_kind == MASK_BLOCKS) first_key = (pos / mask_size) * mask_size;
+    const Reach reach(pos, mask_kind, mask_size, extras.pool);
 
     float* qs = q_smem + warp * dim;
     const T* qrow = q + (int64_t)row * q_stride + (int64_t)head * dim;
@@ -84,26 +115,31 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
     const PageLayout layout(kv_heads, kv_head, page_size, dim, vdim, keys_per_value);
     const int64_t page_elems = layout.page_elems;
     const int vrow = layout.value_row;
-    const T* kbase = cache + (int64_t)kv_head * page_size * dim;
-    const T* vbase = cache + layout.value_base;
+    const int64_t key_base = (int64_t)kv_head * page_size * dim;
     const int* table = block_table + (int64_t)seq * bt_stride;
+    const int* pool_table = extras.pool_table == nullptr ? nullptr : extras.pool_table + (int64_t)seq * extras.pool_bt_stride;
+    const T* pool_cache = reinterpret_cast<const T*>(extras.pool_cache);
 
-    float m = sink ? 0.0f : -1.0e30f;
-    float l = sink ? 1.0f : 0.0f;
+    const bool starts = sink || extras.sinks != nullptr;
+    float m = starts ? (extras.sinks != nullptr ? extras.sinks[head] : 0.0f) : -1.0e30f;
+    float l = starts ? 1.0f : 0.0f;
     float acc[NCV];
 #pragma unroll
     for (int c = 0; c < NCV; ++c) acc[c] = 0.0f;
 
-    for (int key0 = first_key; key0 <= pos; key0 += 32) {
-        const int key = key0 + lane;
-        const bool valid = key <= pos;
-        int64_t v_offset = 0;
+    for (int v0 = 0; v0 < reach.total; v0 += 32) {
+        const int at = v0 + lane;
+        const bool valid = at < reach.total;
+        int64_t v_row = 0;                            // the address of the key's value row
         float s = -1.0e30f;
         if (valid) {
-            const int64_t page = table[key / page_size];
+            const bool averaged = at < reach.pooled;
+            const int key = averaged ? at : reach.first_key + at - reach.pooled;
+            const T* from = averaged ? pool_cache : cache;
+            const int64_t page = (averaged ? pool_table : table)[key / page_size];
             const int in_page = key % page_size;
-            v_offset = page * page_elems + (int64_t)in_page * vrow;
-            const T* kp = kbase + page * page_elems + (int64_t)in_page * dim;
+            v_row = (int64_t)(from + layout.value_base + page * page_elems + (int64_t)in_page * vrow);
+            const T* kp = from + key_base + page * page_elems + (int64_t)in_page * dim;
             float dot = 0.0f;
             if (VEC) {
                 constexpr int N = Packet<T>::N;
@@ -116,7 +152,7 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
             } else {
                 for (int i = 0; i < dim; ++i) dot = fmaf(qs[i], Elem<T>::load(kp + i), dot);
             }
-            s = dot * scale;
+            s = capped(dot * scale, extras.softcap);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.0f;
@@ -124,11 +160,10 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
         l = l * corr + warp_sum(p);
 #pragma unroll
         for (int c = 0; c < NCV; ++c) acc[c] *= corr;
-        const int keys_here = min(32, pos - key0 + 1);
+        const int keys_here = min(32, reach.total - v0);
         for (int j = 0; j < keys_here; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
-            const int64_t off = __shfl_sync(0xffffffffu, v_offset, j);
-            const T* vp = vbase + off;
+            const T* vp = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, v_row, j));
 #pragma unroll
             for (int c = 0; c < NCV; ++c) {
                 const int col = c * 32 + lane;
@@ -171,7 +206,8 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
                                 const T* __restrict__ cache, const int* __restrict__ positions,
                                 const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride,
                                 int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
-                                int mask_size, int sink, float scale, int lv, int keys_per_value, int out_f32) {
+                                int mask_size, int sink, float scale, int lv, int keys_per_value, int out_f32,
+                                MaskExtras extras) {
     constexpr int N = Packet<T>::N;
     constexpr bool SPLIT = SPLITW > 0;
     constexpr int WARPS = SPLIT ? SPLITW : kRowsPerBlock;
@@ -183,15 +219,13 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
     const int head0 = blockIdx.y * HPW;
     if (!SPLIT && row >= rows) return;                // the whole warp leaves; no block-wide barrier on this path
     const size_t per_warp = 32 * sizeof(int64_t) + (size_t)HPW * (32 + dim) * sizeof(float);
-    int64_t* voffs = reinterpret_cast<int64_t*>(smem_raw + warp * per_warp);
+    int64_t* voffs = reinterpret_cast<int64_t*>(smem_raw + warp * per_warp);      // addresses of the keys' value rows
     float* ps = reinterpret_cast<float*>(voffs + 32);         // [HPW][32]
     float* qs = ps + HPW * 32;                                // [HPW][dim]
     const int kv_head = head0 / (heads / kv_heads);
     const int pos = positions[row];
     const int seq = seq_of_row[row];
-    int first_key = 0;
-    if (mask_kind == MASK_WINDOW) first_key = pos - mask_size + 1 > 0 ? pos - mask_size + 1 : 0;
-    else if (mask_kind == MASK_BLOCKS) first_key = (pos / mask_size) * mask_size;
+    const Reach reach(pos, mask_kind, mask_size, extras.pool);
 
     const T* qrow = q + (int64_t)row * q_stride + (int64_t)head0 * dim;       // the HPW heads lie side by side
     for (int i = lane * N; i < HPW * dim; i += 32 * N) Packet<T>::load(qrow + i, qs + i);
@@ -200,17 +234,18 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
     const PageLayout layout(kv_heads, kv_head, page_size, dim, vdim, keys_per_value);
     const int64_t page_elems = layout.page_elems;
     const int vrow = layout.value_row;
-    const T* kbase = cache + (int64_t)kv_head * page_size * dim;
-    const T* vbase = cache + layout.value_base;
+    const int64_t key_base = (int64_t)kv_head * page_size * dim;
     const int* table = block_table + (int64_t)seq * bt_stride;
+    const int* pool_table = extras.pool_table == nullptr ? nullptr : extras.pool_table + (int64_t)seq * extras.pool_bt_stride;
+    const T* pool_cache = reinterpret_cast<const T*>(extras.pool_cache);
     const int vg = lane / lv, vs = lane % lv;         // value phase: group vg owns keys vg, vg + 32 / lv, ...
     const int value_step = 32 / lv;
 
     float m[HPW], l[HPW], acc[HPW][NP][N];
-    const bool starts = sink && (!SPLIT || warp == 0);        // the sink is the start of one running softmax
+    const bool starts = (sink || extras.sinks != nullptr) && (!SPLIT || warp == 0);       // the sink is the start of one running softmax
 #pragma unroll
     for (int h = 0; h < HPW; ++h) {
-        m[h] = starts ? 0.0f : -1.0e30f;
+        m[h] = starts ? (extras.sinks != nullptr ? extras.sinks[head0 + h] : 0.0f) : -1.0e30f;
         l[h] = starts ? 1.0f : 0.0f;
 #pragma unroll
         for (int pk = 0; pk < NP; ++pk)
@@ -218,15 +253,17 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
             for (int e = 0; e < N; ++e) acc[h][pk][e] = 0.0f;
     }
 
-    for (int key0 = first_key + (SPLIT ? 32 * warp : 0); key0 <= pos; key0 += SPLIT ? 32 * WARPS : 32) {
-        const int key = key0 + lane;
-        const bool valid = key <= pos;
-        const int k = valid ? key : pos;              // (a lane behind the last key points at the last key)
-        const int64_t base = (int64_t)table[k / page_size] * page_elems;
+    for (int v0 = SPLIT ? 32 * warp : 0; v0 < reach.total; v0 += SPLIT ? 32 * WARPS : 32) {
+        const bool valid = v0 + lane < reach.total;
+        const int at = valid ? v0 + lane : reach.total - 1;       // (a lane behind the last key points at the last key)
+        const bool averaged = at < reach.pooled;
+        const int k = averaged ? at : reach.first_key + at - reach.pooled;
+        const T* from = averaged ? pool_cache : cache;
+        const int64_t base = (int64_t)(averaged ? pool_table : table)[k / page_size] * page_elems;
         const int in_page = k % page_size;
-        const T* kp = kbase + base + (int64_t)in_page * dim;
+        const T* kp = from + key_base + base + (int64_t)in_page * dim;
         __syncwarp();                                 // the value phase of the block before has read voffs and ps
-        voffs[lane] = base + (int64_t)in_page * vrow;
+        voffs[lane] = (int64_t)(from + layout.value_base + base + (int64_t)in_page * vrow);
         // scores: a lane a key, the key's packets against the HPW queries in shared memory
         float dot[HPW];
 #pragma unroll
@@ -250,7 +287,7 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
         float corr[HPW];
 #pragma unroll
         for (int h = 0; h < HPW; ++h) {
-            const float s = valid ? dot[h] * scale : -1.0e30f;
+            const float s = valid ? capped(dot[h] * scale, extras.softcap) : -1.0e30f;
             const float m_new = fmaxf(m[h], warp_max(s));
             const float p = valid ? __expf(s - m_new) : 0.0f;
             corr[h] = __expf(m[h] - m_new);
@@ -266,11 +303,11 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
 #pragma unroll
                 for (int e = 0; e < N; ++e) acc[h][pk][e] *= corr[h];
         // values: group vg takes keys vg, vg + value_step, ...; a key behind the last one has weight 0
-        const int keys_here = min(32, pos - key0 + 1);
+        const int keys_here = min(32, reach.total - v0);
 #pragma unroll 2
         for (int j0 = 0; j0 < keys_here; j0 += value_step) {
             const int j = j0 + vg;                    // (j < 32 always)
-            const T* vp = vbase + voffs[j];
+            const T* vp = reinterpret_cast<const T*>(voffs[j]);
             float pj[HPW];
 #pragma unroll
             for (int h = 0; h < HPW; ++h) pj[h] = ps[h * 32 + j];
@@ -381,7 +418,7 @@ template <typename T, int HPW, int NP, int SPLITW>
 int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out,
                       int64_t out_stride, const void* cache, const int* positions, const int* seq_of_row,
                       const int* block_table, int bt_stride, int rows, int heads, int kv_heads, int dim, int vdim,
-                      int page_size, int mask_kind, int mask_size, int sink, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
+                      int page_size, int mask_kind, int mask_size, int sink, float scale, int keys_per_value, int out_f32, MaskExtras extras, cudaStream_t stream) {
     constexpr int N = Packet<T>::N;
     int lv = 1;
     while (lv < 32 && lv * NP < vdim / N) lv <<= 1;
@@ -398,7 +435,7 @@ int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t
     cudaError_t launched = tb_launch_pdl(kernel, grid, dim3(WARPS * 32), smem, stream, (const T*)q, q_stride,
                                          (const T*)gate, gate_stride, (T*)out, out_stride, (const T*)cache, positions,
                                          seq_of_row, block_table, bt_stride, rows, heads, kv_heads, dim, vdim,
-                                         page_size, mask_kind, mask_size, sink, scale, lv, keys_per_value, out_f32);
+                                         page_size, mask_kind, mask_size, sink, scale, lv, keys_per_value, out_f32, extras);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
@@ -406,15 +443,15 @@ template <typename T>
 int launch_packets(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
                    const void* cache, const int* positions, const int* seq_of_row, const int* block_table,
                    int bt_stride, int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
-                   int mask_size, int sink, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
+                   int mask_size, int sink, float scale, int keys_per_value, int out_f32, MaskExtras extras, cudaStream_t stream) {
     const int per = heads / kv_heads;
     const bool two = vdim / Packet<T>::N > 32;        // more value packets than lanes: two a lane
     // (which form runs depends on the step's row count and the mask alone)
-    const bool long_span = rows <= kLongMaxRows && (mask_kind == MASK_CAUSAL || mask_size > kLongSpan);
+    const bool long_span = rows <= kLongMaxRows && (mask_kind == MASK_CAUSAL || mask_kind == MASK_WINDOW_POOLED || mask_size > kLongSpan);
 #define TB_PACKETS_AS(HPW, NP, SPLITW)                                                                               \
     launch_packets_as<T, HPW, NP, SPLITW>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions,         \
                                           seq_of_row, block_table, bt_stride, rows, heads, kv_heads, dim, vdim,      \
-                                          page_size, mask_kind, mask_size, sink, scale, keys_per_value, out_f32, stream)
+                                          page_size, mask_kind, mask_size, sink, scale, keys_per_value, out_f32, extras, stream)
 #define TB_PACKETS(HPW, NP)                                                                                          \
     return rows > kSplitMaxRows ? TB_PACKETS_AS(HPW, NP, 0)                                                          \
                                 : (long_span ? TB_PACKETS_AS(HPW, NP, kSplitWarpsLong) : TB_PACKETS_AS(HPW, NP, kSplitWarps))
@@ -431,14 +468,14 @@ template <typename T, bool VEC>
 int launch_vec(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
                const void* cache, const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
                int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind, int mask_size,
-               int sink, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
+               int sink, float scale, int keys_per_value, int out_f32, MaskExtras extras, cudaStream_t stream) {
     const dim3 grid(rows, (heads + kWarps - 1) / kWarps);
     const size_t smem = (size_t)kWarps * dim * sizeof(float);
 #define TB_LAUNCH(NCV)                                                                                              \
     tb_launch_pdl(attention_masked_kernel<T, NCV, VEC>, grid, dim3(kWarps * 32), smem, stream, (const T*)q, q_stride,   \
                   (const T*)gate, gate_stride, (T*)out, out_stride, (const T*)cache, positions, seq_of_row,         \
                   block_table, bt_stride, heads, kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink, scale, keys_per_value, \
-                  out_f32)
+                  out_f32, extras)
     if (vdim <= 32) TB_LAUNCH(1);
     else if (vdim <= 64) TB_LAUNCH(2);
     else if (vdim <= 96) TB_LAUNCH(3);
@@ -454,7 +491,7 @@ template <typename T>
 int launch(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
            const void* cache, const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
            int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind, int mask_size, int sink,
-           float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
+           float scale, int keys_per_value, int out_f32, MaskExtras extras, cudaStream_t stream) {
     // 16-byte key loads need every key row to start on a 16-byte boundary
     const bool vec = dim % Packet<T>::N == 0 && vdim % Packet<T>::N == 0 && (uintptr_t)cache % 16 == 0;
     const uintptr_t bits = (uintptr_t)q | (uintptr_t)gate | (uintptr_t)out;
@@ -463,30 +500,41 @@ int launch(const void* q, int64_t q_stride, const void* gate, int64_t gate_strid
     if (vec && rows_in_packets && vdim <= 64 * Packet<T>::N && dim <= 64 * Packet<T>::N)
         return launch_packets<T>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                  block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
-                                 mask_size, sink, scale, keys_per_value, out_f32, stream);
+                                 mask_size, sink, scale, keys_per_value, out_f32, extras, stream);
     if (vec)
         return launch_vec<T, true>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                    block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
-                                   mask_size, sink, scale, keys_per_value, out_f32, stream);
+                                   mask_size, sink, scale, keys_per_value, out_f32, extras, stream);
     return launch_vec<T, false>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                 block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
-                                mask_size, sink, scale, keys_per_value, out_f32, stream);
+                                mask_size, sink, scale, keys_per_value, out_f32, extras, stream);
 }
 
 }  // namespace
 
 // q: [rows, heads * dim] (row stride q_stride, elements); gate: null or [rows, heads * vdim] (row stride
 // gate_stride); out: [rows, heads * vdim], float32 if out_f32 (out_stride then counts floats) and else the dtype of q;
-// cache: this layer's pages, laid out as keys_per_value says (PageLayout).  mask_kind: 0 causal, 1 window, 2 blocks.
+// cache: this layer's pages, laid out as keys_per_value says (PageLayout).  mask_kind: 0 causal, 1 window, 2 blocks,
+// 3 window with pooled blocks (pool_cache: the layer's pages of averaged keys and values, pool_table: the requests'
+// tables of those pages with row stride pool_bt_stride, pool: tokens a block).  sinks: null or float32 [heads];
+// softcap: 0 for none.
 TB_EXPORT int tb_attention_masked(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out,
                                   int64_t out_stride, const void* cache, const int* positions, const int* seq_of_row,
                                   const int* block_table, int bt_stride, int rows, int heads, int kv_heads, int dim,
                                   int vdim, int page_size, int mask_kind, int mask_size, int sink, float scale,
-                                  int keys_per_value, int out_f32, int dtype, cudaStream_t stream) {
+                                  int keys_per_value, int out_f32, const float* sinks, float softcap,
+                                  const void* pool_cache, const int* pool_table, int pool_bt_stride, int pool, int dtype,
+                                  cudaStream_t stream) {
     if (rows == 0) return 0;
+    if (mask_kind == MASK_WINDOW_POOLED && (pool < 1 || pool_cache == nullptr || pool_table == nullptr || keys_per_value != 1))
+        return TB_ERR_BAD_SIZE;
+    if (softcap < 0.0f) return TB_ERR_BAD_SIZE;
+    MaskExtras extras;
+    extras.sinks = sinks; extras.softcap = softcap; extras.pool_cache = pool_cache; extras.pool_table = pool_table;
+    extras.pool_bt_stride = pool_bt_stride; extras.pool = pool;
     if (dim < 1 || dim > 1024 || vdim < 1 || vdim > 512) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || page_size < 1) return TB_ERR_BAD_SIZE;
-    if (mask_kind < MASK_CAUSAL || mask_kind > MASK_BLOCKS) return TB_ERR_BAD_SIZE;
+    if (mask_kind < MASK_CAUSAL || mask_kind > MASK_WINDOW_POOLED) return TB_ERR_BAD_SIZE;
     if (mask_kind != MASK_CAUSAL && mask_size < 1) return TB_ERR_BAD_SIZE;
     if ((heads + kWarps - 1) / kWarps > 65535) return TB_ERR_BAD_SIZE;
     if (keys_per_value < 0 || (keys_per_value > 0 && kv_heads % keys_per_value != 0)) return TB_ERR_BAD_SIZE;
@@ -494,10 +542,10 @@ TB_EXPORT int tb_attention_masked(const void* q, int64_t q_stride, const void* g
     if (dtype == TB_F32)
         return launch<float>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row, block_table,
                              bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink, scale,
-                             keys_per_value, out_f32, stream);
+                             keys_per_value, out_f32, extras, stream);
     if (dtype == TB_BF16)
         return launch<__nv_bfloat16>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                      block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
-                                     mask_size, sink, scale, keys_per_value, out_f32, stream);
+                                     mask_size, sink, scale, keys_per_value, out_f32, extras, stream);
     return TB_ERR_BAD_DTYPE;
 }

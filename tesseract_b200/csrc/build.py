@@ -64,6 +64,7 @@ SOURCES: Dict[str, List[str]] = {
     "differential": [],
     "latent_rope_cache": [],
     "attention_latent_mma": [],
+    "gated_residual": [],
 }
 
 

@@ -3,6 +3,10 @@
 //
 //   tb_choose_topk     from the router's 32-bit logits (a product kernel left them): the `top` largest of a row,
 //                      largest first (the lowest index wins a tie), and the softmax over those alone.
+//   tb_choose_grouped  the softmax over all of a row's logits; the experts form `groups` equal runs of neighbours, a
+//                      group counts as much as its best expert, only experts of the `keep` best groups can be chosen;
+//                      of those the `top` with the largest scores, largest first (the lowest index wins a tie), weighted
+//                      by their scores over the chosen scores' sum (+ 1e-20), times `weight_scale`.
 //   tb_expert_plan     rows * top assignments (row t, slot s -> assignment t * top + s) are grouped by their expert:
 //                      offsets[e] .. offsets[e + 1] of `order` name the assignments of expert e.
 //   tb_expert_linear   out[a, :] = act(W[expert(a)] in[source(a), :]) for every assignment a, a tile of one expert's
@@ -69,6 +73,89 @@ choose_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, floa
     for (int e = lane; e < experts; e += 32) zs[e] = logits[(int64_t)row * experts + e];
     __syncwarp();
     choose_top(zs, experts, top, ids + (int64_t)row * top, weights + (int64_t)row * top, lane);
+}
+
+
+// A warp a row; logits 32-bit [rows, experts].  Shared memory per warp: the row's scores, then one flag per group.
+__global__ void __launch_bounds__(kRouteWarps * 32)
+choose_grouped_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights, int rows,
+                      int experts, int top, int groups, int keep, float weight_scale) {
+    extern __shared__ __align__(16) float route_smem[];
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kRouteWarps + warp;
+    if (row >= rows) return;
+    float* zs = route_smem + (size_t)warp * (experts + groups);
+    float* best_of = zs + experts;                               // a group's best score; -inf once the group is kept
+    const int per = experts / groups;
+    float top_logit = -INFINITY;
+    for (int e = lane; e < experts; e += 32) top_logit = fmaxf(top_logit, logits[(int64_t)row * experts + e]);
+    top_logit = warp_max(top_logit);
+    float total = 0.0f;
+    for (int e = lane; e < experts; e += 32) {
+        const float p = expf(logits[(int64_t)row * experts + e] - top_logit);
+        zs[e] = p;
+        total += p;
+    }
+    total = warp_sum(total);
+    __syncwarp();
+    const float inv_total = 1.0f / total;
+    for (int e = lane; e < experts; e += 32) zs[e] *= inv_total;
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+        float best = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, zs[e]);
+        best_of[g] = best;
+    }
+    __syncwarp();
+    // the `keep` best groups, one after the other (the lowest index among equals); the experts of all others leave
+    for (int k = 0; k < keep; ++k) {
+        float best = -INFINITY;
+        int where = 0x7fffffff;
+        for (int g = lane; g < groups; g += 32) {
+            const float v = best_of[g];
+            if (v > best) { best = v; where = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int ow = __shfl_xor_sync(0xffffffffu, where, o);
+            if (ob > best || (ob == best && ow < where)) { best = ob; where = ow; }
+        }
+        if (lane == 0 && where != 0x7fffffff) best_of[where] = -INFINITY;
+        __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+        if (best_of[e / per] != -INFINITY) zs[e] = -INFINITY;       // (a kept group's entry was set to -inf above)
+    __syncwarp();
+    int* my_ids = ids + (int64_t)row * top;
+    float* my_weights = weights + (int64_t)row * top;
+    float chosen_sum = 0.0f;
+    for (int s = 0; s < top; ++s) {
+        float best = -INFINITY;
+        int where = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = zs[e];
+            if (v > best) { best = v; where = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int ow = __shfl_xor_sync(0xffffffffu, where, o);
+            if (ob > best || (ob == best && ow < where)) { best = ob; where = ow; }
+        }
+        if (where == 0x7fffffff) { where = 0; best = 0.0f; }     // (fewer allowed experts than `top`, or NaN logits)
+        chosen_sum += best;
+        if (lane == 0) {
+            my_ids[s] = where;
+            my_weights[s] = best;
+            zs[where] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    const float factor = weight_scale / (chosen_sum + 1e-20f);
+    for (int s = lane; s < top; s += 32) my_weights[s] *= factor;
 }
 
 // ----------------------------------------------------------------------------- grouping
@@ -508,6 +595,20 @@ TB_EXPORT int tb_choose_topk(const float* logits, int* ids, float* weights, int 
     if (smem > 40 * 1024) return TB_ERR_BAD_SIZE;
     cudaError_t launched = tb_launch_pdl(choose_topk_kernel, dim3((rows + kRouteWarps - 1) / kRouteWarps),
                                          dim3(kRouteWarps * 32), smem, stream, logits, ids, weights, rows, experts, top);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+// logits: 32-bit [rows, experts], contiguous; `groups` divides `experts`, keep <= groups, top <= keep * experts / groups.
+TB_EXPORT int tb_choose_grouped(const float* logits, int* ids, float* weights, int rows, int experts, int top, int groups,
+                                int keep, float weight_scale, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (experts < 1 || top < 1 || groups < 1 || experts % groups != 0 || keep < 1 || keep > groups) return TB_ERR_BAD_SIZE;
+    if (top > keep * (experts / groups)) return TB_ERR_BAD_SIZE;
+    const size_t smem = (size_t)kRouteWarps * (experts + groups) * sizeof(float);
+    if (smem > 40 * 1024) return TB_ERR_BAD_SIZE;
+    cudaError_t launched = tb_launch_pdl(choose_grouped_kernel, dim3((rows + kRouteWarps - 1) / kRouteWarps),
+                                         dim3(kRouteWarps * 32), smem, stream, logits, ids, weights, rows, experts, top,
+                                         groups, keep, weight_scale);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 

@@ -8,7 +8,8 @@
 // of a head are written by the product in front, this kernel fills in the head's rotated part.
 //
 // Rotation: neighbouring pairs (2i, 2i + 1) of the first rot_dims numbers of the rotated part turn by
-// position * inv_freq[i]; angle, sine, cosine and the norm are 32-bit; every stored number is rounded once.
+// position * inv_freq[i], cosine and sine both multiplied by `amplitude`; angle, sine, cosine and the norm are 32-bit;
+// every stored number is rounded once.
 #include "common.cuh"
 
 namespace {
@@ -20,7 +21,7 @@ latent_rope_cache_kernel(const float* __restrict__ down, int64_t down_stride, co
                          const float* __restrict__ weight, const int* __restrict__ positions,
                          const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride,
                          const float* __restrict__ inv_freq, int heads, int dim, int rank, int rot_width, int rot_dims,
-                         int page_size, float eps) {
+                         int page_size, float eps, float amplitude) {
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
@@ -60,6 +61,8 @@ latent_rope_cache_kernel(const float* __restrict__ down, int64_t down_stride, co
         if (c + 1 < rot_dims) {
             float sn, cs;
             sincosf((float)pos * inv_freq[i], &sn, &cs);
+            sn *= amplitude;
+            cs *= amplitude;
             Elem<T>::store(to, u * cs - v * sn);
             Elem<T>::store(to + 1, v * cs + u * sn);
         } else {
@@ -77,7 +80,7 @@ TB_EXPORT int tb_latent_rope_cache(const float* down, int64_t down_stride, const
                                    int64_t full_stride, void* cache, const float* weight, const int* positions,
                                    const int* seq_of_row, const int* block_table, int bt_stride, const float* inv_freq,
                                    int rows, int heads, int dim, int rank, int rot_width, int rot_dims, int page_size,
-                                   float eps, int dtype, cudaStream_t stream) {
+                                   float eps, float amplitude, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
     if (heads < 1 || dim < 0 || rank < 1 || rot_width < 0 || page_size < 1) return TB_ERR_BAD_SIZE;
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > rot_width || (rot_dims > 0 && inv_freq == nullptr)) return TB_ERR_BAD_SIZE;
@@ -86,12 +89,12 @@ TB_EXPORT int tb_latent_rope_cache(const float* down, int64_t down_stride, const
         launched = tb_launch_pdl(latent_rope_cache_kernel<float>, dim3(rows), dim3(256), 0, stream, down, down_stride,
                                  (const float*)q, q_stride, (float*)q_full, full_stride, (float*)cache, weight, positions,
                                  seq_of_row, block_table, bt_stride, inv_freq, heads, dim, rank, rot_width, rot_dims,
-                                 page_size, eps);
+                                 page_size, eps, amplitude);
     else if (dtype == TB_BF16)
         launched = tb_launch_pdl(latent_rope_cache_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, down,
                                  down_stride, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)q_full, full_stride,
                                  (__nv_bfloat16*)cache, weight, positions, seq_of_row, block_table, bt_stride, inv_freq,
-                                 heads, dim, rank, rot_width, rot_dims, page_size, eps);
+                                 heads, dim, rank, rot_width, rot_dims, page_size, eps, amplitude);
     else
         return TB_ERR_BAD_DTYPE;
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;

@@ -1,5 +1,10 @@
 // Linear attention with a fixed decay per head:  S_t = a S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t  (S: [dim, vdim], 32-bit,
-// kept per request in its state slot), with q = silu(.), k = silu(.), v = silu(.) of the projected rows.
+// kept per request in its state slot), with q = silu(.), k = silu(.), v = silu(.) of the projected rows, or, for a
+// mixer that rotates its queries and keys (retention), of rows that tb_retention_prepare left in 32-bit:
+//
+//   tb_retention_prepare   q and k heads turned in the rotate-half layout by position * inv_freq[i] (32-bit angle,
+//                          sincosf), k times k_scale, v copied; everything widened to 32-bit
+//   tb_head_norm_gate      o / sqrt(mean(o^2) + eps) per head (no weight), times silu or sigmoid of a gate row
 //
 // A block takes one (sequence, head, slice of 32 value columns) and walks the sequence's rows of this step in chunks of
 // up to C rows.  With S the state at the chunk's start and rows 0 .. c-1 of the chunk,
@@ -30,6 +35,10 @@ static_assert(kRows == 8, "the vector forms below are written for eight");
 
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 
+// What q, k and v go through before the recurrence: ACT_SILU, or ACT_NONE for rows that a kernel in front prepared.
+enum RowActivation : int { ACT_NONE = 0, ACT_SILU = 1 };
+__device__ __forceinline__ float activate(float z, int act) { return act == ACT_SILU ? silu(z) : z; }
+
 // Floats of a query or key row in shared memory.  Where dim is a multiple of four, rows start on 16 bytes and are read
 // four numbers at a time (the padding of four keeps a quarter-warp's rows on different banks); otherwise a number at a time.
 __host__ __device__ __forceinline__ int row_floats(int dim) { return dim % 4 == 0 ? dim + 4 : dim + 1; }
@@ -47,11 +56,11 @@ __device__ __forceinline__ float dot_in_order(const float* a, const float* b, in
     return sum;
 }
 
-// dst[t][0 .. n) = silu(src[t][0 .. valid)) and zeros behind, for c rows (src rows `stride` elements apart, dst rows
+// dst[t][0 .. n) = act(src[t][0 .. valid)) and zeros behind, for c rows (src rows `stride` elements apart, dst rows
 // `dst_stride` floats): with PACKETS 16 bytes of the source at a time where its rows allow it, else an element at a time.
 template <typename T, bool PACKETS>
 __device__ __forceinline__ void load_silu_rows(float* dst, int dst_stride, const T* src, int64_t stride, int c, int n,
-                                               int valid) {
+                                               int valid, int act) {
     constexpr int N = Packet<T>::N;
     if (PACKETS && n % N == 0 && valid % N == 0 && stride % N == 0 && (uintptr_t)src % 16 == 0) {
         const int packets = n / N;
@@ -61,7 +70,7 @@ __device__ __forceinline__ void load_silu_rows(float* dst, int dst_stride, const
             if (i < valid) {
                 Packet<T>::load(src + (int64_t)t * stride + i, v);
 #pragma unroll
-                for (int u = 0; u < N; ++u) v[u] = silu(v[u]);
+                for (int u = 0; u < N; ++u) v[u] = activate(v[u], act);
             } else {
 #pragma unroll
                 for (int u = 0; u < N; ++u) v[u] = 0.0f;
@@ -72,7 +81,7 @@ __device__ __forceinline__ void load_silu_rows(float* dst, int dst_stride, const
     } else {
         for (int e = threadIdx.x; e < c * n; e += kThreads) {
             const int t = e / n, i = e % n;
-            dst[t * dst_stride + i] = i < valid ? silu(Elem<T>::load(src + (int64_t)t * stride + i)) : 0.0f;
+            dst[t * dst_stride + i] = i < valid ? activate(Elem<T>::load(src + (int64_t)t * stride + i), act) : 0.0f;
         }
     }
 }
@@ -101,7 +110,7 @@ __global__ void __launch_bounds__(kThreads)
 lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int k_off, int v_off,
                  const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ out,
                  const int* __restrict__ row_start, const int* __restrict__ state_slots, int heads, int dim, int vdim,
-                 int chunk, const float* __restrict__ tile_state, int num_seqs) {
+                 int chunk, const float* __restrict__ tile_state, int num_seqs, int act) {
     extern __shared__ __align__(16) float smem[];
     pdl_trigger();
     const int head = blockIdx.y, col0 = blockIdx.z * kSlice;
@@ -138,9 +147,9 @@ lightning_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int
         const int c = min(chunk, last - row0);
         __syncthreads();                           // the chunk before is done with qs, ks, vs, A (and S is written)
         const T* rows_at = proj + (int64_t)row0 * proj_stride;
-        load_silu_rows<T, WIDE>(qs, dpad, rows_at + q_off + (int64_t)head * dim, proj_stride, c, dim, dim);
-        load_silu_rows<T, WIDE>(ks, dpad, rows_at + k_off + (int64_t)head * dim, proj_stride, c, dim, dim);
-        load_silu_rows<T, WIDE>(vs, kSlice, rows_at + v_off + (int64_t)head * vdim + col0, proj_stride, c, kSlice, cols);
+        load_silu_rows<T, WIDE>(qs, dpad, rows_at + q_off + (int64_t)head * dim, proj_stride, c, dim, dim, act);
+        load_silu_rows<T, WIDE>(ks, dpad, rows_at + k_off + (int64_t)head * dim, proj_stride, c, dim, dim, act);
+        load_silu_rows<T, WIDE>(vs, kSlice, rows_at + v_off + (int64_t)head * vdim + col0, proj_stride, c, kSlice, cols, act);
         __syncthreads();
         // scores of the chunk: thread e takes (t, s) with s fastest, so neighbouring lanes read neighbouring key rows
         for (int e = threadIdx.x; e < c * c; e += kThreads) {
@@ -268,7 +277,8 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 lightning_step_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int k_off, int v_off,
                       const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ out,
-                      const int* __restrict__ row_start, const int* __restrict__ state_slots, int heads, int dim, int vdim) {
+                      const int* __restrict__ row_start, const int* __restrict__ state_slots, int heads, int dim, int vdim,
+                      int act) {
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                              // [dim]
     float* ks = qs + dim;                          // [dim]
@@ -283,11 +293,11 @@ lightning_step_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off
     if (row >= row_start[seq + 1]) return;
     const T* p = proj + (int64_t)row * proj_stride + (int64_t)head * dim;
     for (int i = threadIdx.x; i < dim; i += kThreads) {
-        qs[i] = silu(Elem<T>::load(p + q_off + i));
-        ks[i] = silu(Elem<T>::load(p + k_off + i));
+        qs[i] = activate(Elem<T>::load(p + q_off + i), act);
+        ks[i] = activate(Elem<T>::load(p + k_off + i), act);
     }
     const bool there = col0 + lane < vdim;
-    const float v = there ? silu(Elem<T>::load(proj + (int64_t)row * proj_stride + v_off + (int64_t)head * vdim + col0 + lane)) : 0.0f;
+    const float v = there ? activate(Elem<T>::load(proj + (int64_t)row * proj_stride + v_off + (int64_t)head * vdim + col0 + lane), act) : 0.0f;
     __syncthreads();
     float* slot = state + ((int64_t)state_slots[seq] * heads + head) * dim * vdim + col0 + lane;
     float from_state = 0.0f;
@@ -319,7 +329,8 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 lightning_tile_sum_kernel(const T* __restrict__ proj, int64_t proj_stride, int k_off, int v_off,
                           const float* __restrict__ decay, float* __restrict__ tile_state,
-                          const int* __restrict__ row_start, int num_seqs, int heads, int dim, int vdim, int chunk) {
+                          const int* __restrict__ row_start, int num_seqs, int heads, int dim, int vdim, int chunk,
+                          int act) {
     extern __shared__ __align__(16) float smem[];
     pdl_trigger();
     const int head = blockIdx.y, col0 = blockIdx.z * kSlice;
@@ -335,8 +346,8 @@ lightning_tile_sum_kernel(const T* __restrict__ proj, int64_t proj_stride, int k
     int seq, r0, c;
     if (!find_tile(row_start, num_seqs, chunk, blockIdx.x, seq, r0, c)) return;
     const T* rows_at = proj + (int64_t)r0 * proj_stride;
-    load_silu_rows<T, true>(ks, dpad, rows_at + k_off + (int64_t)head * dim, proj_stride, c, dim, dim);
-    load_silu_rows<T, true>(vs, kSlice, rows_at + v_off + (int64_t)head * vdim + col0, proj_stride, c, kSlice, cols);
+    load_silu_rows<T, true>(ks, dpad, rows_at + k_off + (int64_t)head * dim, proj_stride, c, dim, dim, act);
+    load_silu_rows<T, true>(vs, kSlice, rows_at + v_off + (int64_t)head * vdim + col0, proj_stride, c, kSlice, cols, act);
     __syncthreads();
     const int lane = threadIdx.x & 31, group = threadIdx.x >> 5;
     float* mine = tile_state + ((int64_t)blockIdx.x * heads + head) * dim * vdim;
@@ -401,6 +412,74 @@ lightning_scan_kernel(const float* __restrict__ decay, float* __restrict__ state
     }
 }
 
+
+// ----------------------------------------------------------------------------- around the recurrence
+
+// One warp per (row, head of q, k or v); out row: [H * dim q | H * dim k | H * vdim v], 32-bit.
+template <typename T>
+__global__ void __launch_bounds__(128)
+retention_prepare_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off, int k_off, int v_off,
+                         float* __restrict__ out, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                         int heads, int dim, int vdim, int rot_dims, float amplitude, float k_scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x, slot = blockIdx.y * 4 + warp;
+    if (slot >= 3 * heads) return;
+    const int64_t out_stride = (int64_t)heads * (2 * dim + vdim);
+    const T* prow = proj + (int64_t)row * proj_stride;
+    float* orow = out + (int64_t)row * out_stride;
+    if (slot >= 2 * heads) {
+        const int head = slot - 2 * heads;
+        const T* src = prow + v_off + (int64_t)head * vdim;
+        float* dst = orow + (int64_t)2 * heads * dim + (int64_t)head * vdim;
+        for (int i = lane; i < vdim; i += 32) dst[i] = Elem<T>::load(src + i);
+        return;
+    }
+    const bool is_key = slot >= heads;
+    const int head = is_key ? slot - heads : slot;
+    const T* src = prow + (is_key ? k_off : q_off) + (int64_t)head * dim;
+    float* dst = orow + (int64_t)slot * dim;
+    const float factor = is_key ? k_scale : 1.0f;
+    const float pos = (float)positions[row];
+    const int half = rot_dims >> 1;
+    for (int i = lane; i < half; i += 32) {
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        sn *= amplitude;
+        cs *= amplitude;
+        const float u = Elem<T>::load(src + i), v = Elem<T>::load(src + i + half);
+        dst[i] = (u * cs - v * sn) * factor;
+        dst[i + half] = (v * cs + u * sn) * factor;
+    }
+    for (int i = rot_dims + lane; i < dim; i += 32) dst[i] = Elem<T>::load(src + i) * factor;
+}
+
+enum GateKind : int { GATE_SIGMOID = 0, GATE_SILU = 1 };
+
+// One warp per (row, head): the head's 32-bit numbers over their root mean square, times the activated gate.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int64_t gate_stride, T* __restrict__ out,
+                      int64_t out_stride, int heads, int vdim, float eps, int gate_kind) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x, head = blockIdx.y * 4 + warp;
+    if (head >= heads) return;
+    const float* orow = o + ((int64_t)row * heads + head) * vdim;
+    float ss = 0.0f;
+    for (int i = lane; i < vdim; i += 32) ss = fmaf(orow[i], orow[i], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)vdim + eps);
+    const T* grow = gate + (int64_t)row * gate_stride + (int64_t)head * vdim;
+    T* dst = out + (int64_t)row * out_stride + (int64_t)head * vdim;
+    for (int i = lane; i < vdim; i += 32) {
+        const float g = Elem<T>::load(grow + i);
+        const float s = 1.0f / (1.0f + expf(-g));
+        Elem<T>::store(dst + i, orow[i] * inv * (gate_kind == GATE_SILU ? g * s : s));
+    }
+}
+
 size_t smem_for(int chunk, int dim) {
     return sizeof(float) * ((size_t)2 * chunk * row_floats(dim) + (size_t)chunk * kSlice + (size_t)chunk * chunk +
                             (size_t)dim * kSlice + chunk + 1);
@@ -423,7 +502,7 @@ int tiles_for(int rows, int num_seqs, int dim, int max_new) {
 template <typename T>
 int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_off, const float* decay, float* state,
            float* out, const int* row_start, const int* state_slots, int rows, int num_seqs, int heads, int dim, int vdim,
-           int max_new, float* tile_state, cudaStream_t stream) {
+           int max_new, float* tile_state, int act, cudaStream_t stream) {
     const int chunk = chunk_for(dim, max_new);
     const size_t smem = smem_for(chunk, dim);
     if (smem > 220 * 1024) return TB_ERR_BAD_SIZE;
@@ -438,14 +517,14 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
         if (step_smem > 40 * 1024) return TB_ERR_BAD_SIZE;
         cudaError_t launched = tb_launch_pdl(lightning_step_kernel<T>, dim3(num_seqs, heads, slices), dim3(kThreads),
                                              step_smem, stream, (const T*)proj, proj_stride, q_off, k_off, v_off, decay,
-                                             state, out, row_start, state_slots, heads, dim, vdim);
+                                             state, out, row_start, state_slots, heads, dim, vdim, act);
         return launched == cudaSuccess ? tb_launch_status() : (int)launched;
     }
     const int tiles = tiles_for(rows, num_seqs, dim, max_new);
     if (tiles == 0) {
         cudaError_t launched = tb_launch_pdl(kernel, dim3(num_seqs, heads, slices), dim3(kThreads), smem, stream,
                                              (const T*)proj, proj_stride, q_off, k_off, v_off, decay, state, out, row_start,
-                                             state_slots, heads, dim, vdim, chunk, (const float*)nullptr, num_seqs);
+                                             state_slots, heads, dim, vdim, chunk, (const float*)nullptr, num_seqs, act);
         return launched == cudaSuccess ? tb_launch_status() : (int)launched;
     }
     if (tile_state == nullptr) return TB_ERR_BAD_SIZE;
@@ -457,7 +536,7 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
     }
     cudaError_t launched = tb_launch_pdl(sums, dim3(tiles, heads, slices), dim3(kThreads), sums_smem, stream, (const T*)proj,
                                          proj_stride, k_off, v_off, decay, tile_state, row_start, num_seqs, heads, dim,
-                                         vdim, chunk);
+                                         vdim, chunk, act);
     if (launched != cudaSuccess) return (int)launched;
     const int parts = max(1, min(64, (dim * vdim + kThreads - 1) / kThreads));
     launched = tb_launch_pdl(lightning_scan_kernel, dim3(num_seqs, heads, parts), dim3(kThreads), (size_t)0, stream, decay,
@@ -465,7 +544,7 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
     if (launched != cudaSuccess) return (int)launched;
     launched = tb_launch_pdl(kernel, dim3(tiles, heads, slices), dim3(kThreads), smem, stream, (const T*)proj, proj_stride,
                              q_off, k_off, v_off, decay, state, out, row_start, state_slots, heads, dim, vdim, chunk,
-                             (const float*)tile_state, num_seqs);
+                             (const float*)tile_state, num_seqs, act);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
@@ -474,22 +553,69 @@ int launch(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_of
 // proj: [rows, ...] in `dtype`, row stride proj_stride (elements); q at column q_off ([heads, dim]), k at k_off ([heads, dim]),
 // v at v_off ([heads, vdim]), all before their activation.  decay: float32 [heads].  state: float32 [slots, heads, dim, vdim].
 // out: float32 [rows, heads * vdim].  max_new: the most rows any sequence brings (it sizes the chunk).  tile_state: float32
-// [tb_lightning_tiles(...), heads, dim, vdim] of scratch where that count is not 0.
+// [tb_lightning_tiles(...), heads, dim, vdim] of scratch where that count is not 0.  act: 1 applies SiLU to q, k and v as
+// they are read, 0 takes them as they are.
 TB_EXPORT int tb_lightning_tiles(int rows, int num_seqs, int dim, int max_new) {
     return (rows < 1 || num_seqs < 1 || dim < 1 || max_new < 1) ? 0 : tiles_for(rows, num_seqs, dim, max_new);
 }
 
 TB_EXPORT int tb_lightning(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_off, const float* decay,
                            float* state, float* out, const int* row_start, const int* state_slots, int rows, int num_seqs,
-                           int heads, int dim, int vdim, int max_new, float* tile_state, int dtype, cudaStream_t stream) {
+                           int heads, int dim, int vdim, int max_new, float* tile_state, int act, int dtype,
+                           cudaStream_t stream) {
     if (num_seqs == 0 || rows == 0) return 0;
+    if (act != ACT_NONE && act != ACT_SILU) return TB_ERR_BAD_SIZE;
     if (heads < 1 || heads > 65535 || dim < 1 || vdim < 1 || (vdim + kSlice - 1) / kSlice > 65535 || max_new < 1)
         return TB_ERR_BAD_SIZE;
     if (dtype == TB_F32)
         return launch<float>(proj, proj_stride, q_off, k_off, v_off, decay, state, out, row_start, state_slots, rows,
-                             num_seqs, heads, dim, vdim, max_new, tile_state, stream);
+                             num_seqs, heads, dim, vdim, max_new, tile_state, act, stream);
     if (dtype == TB_BF16)
         return launch<__nv_bfloat16>(proj, proj_stride, q_off, k_off, v_off, decay, state, out, row_start, state_slots,
-                                     rows, num_seqs, heads, dim, vdim, max_new, tile_state, stream);
+                                     rows, num_seqs, heads, dim, vdim, max_new, tile_state, act, stream);
     return TB_ERR_BAD_DTYPE;
+}
+
+// proj as for tb_lightning; out: float32 [rows, heads * (2 * dim + vdim)] (q heads, k heads, v heads); inv_freq: float32
+// [rot_dims / 2] (may be null when rot_dims is 0).
+TB_EXPORT int tb_retention_prepare(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_off, float* out,
+                                   const int* positions, const float* inv_freq, int rows, int heads, int dim, int vdim,
+                                   int rot_dims, float amplitude, float k_scale, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (heads < 1 || dim < 1 || vdim < 1 || rot_dims < 0 || rot_dims % 2 || rot_dims > dim) return TB_ERR_BAD_SIZE;
+    if (rot_dims > 0 && inv_freq == nullptr) return TB_ERR_BAD_SIZE;
+    const dim3 grid(rows, (3 * heads + 3) / 4);
+    if (grid.y > 65535) return TB_ERR_BAD_SIZE;
+    cudaError_t launched;
+    if (dtype == TB_F32)
+        launched = tb_launch_pdl(retention_prepare_kernel<float>, grid, dim3(128), (size_t)0, stream, (const float*)proj,
+                                 proj_stride, q_off, k_off, v_off, out, positions, inv_freq, heads, dim, vdim, rot_dims,
+                                 amplitude, k_scale);
+    else if (dtype == TB_BF16)
+        launched = tb_launch_pdl(retention_prepare_kernel<__nv_bfloat16>, grid, dim3(128), (size_t)0, stream,
+                                 (const __nv_bfloat16*)proj, proj_stride, q_off, k_off, v_off, out, positions, inv_freq,
+                                 heads, dim, vdim, rot_dims, amplitude, k_scale);
+    else
+        return TB_ERR_BAD_DTYPE;
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+// o: float32 [rows, heads * vdim], contiguous; gate and out: [rows, >= heads * vdim] in `dtype` with row strides of their own.
+TB_EXPORT int tb_head_norm_gate(const float* o, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
+                                int rows, int heads, int vdim, float eps, int gate_kind, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (heads < 1 || vdim < 1 || (gate_kind != GATE_SIGMOID && gate_kind != GATE_SILU)) return TB_ERR_BAD_SIZE;
+    const dim3 grid(rows, (heads + 3) / 4);
+    if (grid.y > 65535) return TB_ERR_BAD_SIZE;
+    cudaError_t launched;
+    if (dtype == TB_F32)
+        launched = tb_launch_pdl(head_norm_gate_kernel<float>, grid, dim3(128), (size_t)0, stream, o, (const float*)gate,
+                                 gate_stride, (float*)out, out_stride, heads, vdim, eps, gate_kind);
+    else if (dtype == TB_BF16)
+        launched = tb_launch_pdl(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), (size_t)0, stream, o,
+                                 (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride, heads, vdim, eps,
+                                 gate_kind);
+    else
+        return TB_ERR_BAD_DTYPE;
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }

@@ -9,6 +9,8 @@
 //   tb_add_bias           y[t, j] += b[j]                      (y 32-bit or bfloat16, b 32-bit)
 //   tb_scale_rows         y[t, j] *= s                         (32-bit y)
 //   tb_add_rows           a[t, j] += b[t, j]                   (32-bit)
+//   tb_blend_rows         a[t, j] = x * a[t, j] + y * b[t, j]  (32-bit: two mixers side by side, each with a weight)
+//   tb_sigmoid_mul        out[t, j] = a[t, j] * sigmoid(g[t, j])      (an output gate; 32-bit arithmetic)
 //   tb_embedding_scaled   out[t, :] = float(table[token[t], :]) * s   (32-bit out; the table 32-bit or bfloat16)
 //   tb_token_gate         out[t, j] = act(z[t, j]) * table[token[t], offset + j]     (32-bit z; a slice of a second
 //                         embedding table gated by a projection of the stream)
@@ -102,6 +104,25 @@ __global__ void add_rows_kernel(float* __restrict__ a, const float* __restrict__
     pdl_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
         a[i] += b[i];
+}
+
+__global__ void blend_rows_kernel(float* __restrict__ a, const float* __restrict__ b, int64_t total, float x, float y) {
+    pdl_trigger();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+        a[i] = x * a[i] + y * b[i];
+}
+
+template <typename T>
+__global__ void sigmoid_mul_kernel(const T* __restrict__ a, int64_t a_stride, const T* __restrict__ g, int64_t g_stride,
+                                   T* __restrict__ out, int64_t out_stride, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const T* ar = a + (int64_t)blockIdx.x * a_stride;
+    const T* gr = g + (int64_t)blockIdx.x * g_stride;
+    T* o = out + (int64_t)blockIdx.x * out_stride;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < width; j += gridDim.y * blockDim.x)
+        Elem<T>::store(o + j, Elem<T>::load(ar + j) * (1.0f / (1.0f + expf(-Elem<T>::load(gr + j)))));
 }
 
 template <typename T>
@@ -217,6 +238,29 @@ TB_EXPORT int tb_scale_rows(float* y, int64_t total, float s, cudaStream_t strea
 TB_EXPORT int tb_add_rows(float* a, const float* b, int64_t total, cudaStream_t stream) {
     if (total == 0) return 0;
     cudaError_t launched = tb_launch_pdl(add_rows_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, a, b, total);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+TB_EXPORT int tb_blend_rows(float* a, const float* b, int64_t total, float x, float y, cudaStream_t stream) {
+    if (total == 0) return 0;
+    cudaError_t launched = tb_launch_pdl(blend_rows_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, a, b, total, x, y);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+TB_EXPORT int tb_sigmoid_mul(const void* a, int64_t a_stride, const void* g, int64_t g_stride, void* out, int64_t out_stride,
+                             int rows, int width, int dtype, cudaStream_t stream) {
+    if (rows == 0 || width == 0) return 0;
+    const int threads = 256;
+    cudaError_t launched;
+    if (dtype == TB_F32)
+        launched = tb_launch_pdl(sigmoid_mul_kernel<float>, row_grid(rows, width, threads), dim3(threads), 0, stream,
+                                 (const float*)a, a_stride, (const float*)g, g_stride, (float*)out, out_stride, width);
+    else if (dtype == TB_BF16)
+        launched = tb_launch_pdl(sigmoid_mul_kernel<__nv_bfloat16>, row_grid(rows, width, threads), dim3(threads), 0, stream,
+                                 (const __nv_bfloat16*)a, a_stride, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out,
+                                 out_stride, width);
+    else
+        return TB_ERR_BAD_DTYPE;
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 

@@ -11,6 +11,9 @@
 //
 // One warp per (row, head of q, k or v).  All arithmetic is 32-bit; each stored value is rounded once; the order
 // of a head's sum of squares depends on d alone.
+//
+// tb_pool_blocks, for a mixer that also attends to averaged blocks of old tokens, runs behind it: every row that ends a
+// block of `pool` positions leaves the block's averaged key and value in pages of their own.
 #include "common.cuh"
 
 namespace {
@@ -91,6 +94,41 @@ rope_norm_cache_kernel(const T* __restrict__ proj, int64_t proj_stride, T* __res
     for (int i = lane; i < g.dim; i += 32) Elem<T>::store(dst + i, mine[i] * inv);
 }
 
+
+// For every row of the step that ends a block of `pool` positions ((position + 1) % pool == 0): the averages of the block's
+// keys and of its values, as the pages hold them, into entry position / pool of the request's pooled pages (same page
+// layout).  A block of threads per (row, kv head), a thread a column, the block's tokens added in order in 32-bit.
+template <typename T>
+__global__ void __launch_bounds__(128)
+pool_blocks_kernel(const T* __restrict__ cache, T* __restrict__ pool_cache, const int* __restrict__ positions,
+                   const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride,
+                   const int* __restrict__ pool_table, int pool_bt_stride, int kv_heads, int dim, int vdim, int page_size,
+                   int pool) {
+    pdl_trigger();
+    pdl_wait();                                       // the pages were written by the kernel in front
+    const int row = blockIdx.x, g = blockIdx.y;
+    const int pos = positions[row];
+    if ((pos + 1) % pool != 0) return;
+    const int seq = seq_of_row[row];
+    const int entry = pos / pool, first = pos - pool + 1;
+    const int64_t page_elems = (int64_t)kv_heads * page_size * (dim + vdim);
+    const int* table = block_table + (int64_t)seq * bt_stride;
+    const int64_t to_page = (int64_t)pool_table[(int64_t)seq * pool_bt_stride + entry / page_size] * page_elems;
+    const int to_in_page = entry % page_size;
+    for (int col = threadIdx.x; col < dim + vdim; col += blockDim.x) {
+        const bool is_key = col < dim;
+        const int width = is_key ? dim : vdim, c = is_key ? col : col - dim;
+        const int64_t part = is_key ? 0 : (int64_t)kv_heads * page_size * dim;
+        float sum = 0.0f;
+        for (int j = 0; j < pool; ++j) {
+            const int key = first + j;
+            const int64_t page = (int64_t)table[key / page_size] * page_elems;
+            sum += Elem<T>::load(cache + page + part + ((int64_t)g * page_size + key % page_size) * width + c);
+        }
+        Elem<T>::store(pool_cache + to_page + part + ((int64_t)g * page_size + to_in_page) * width + c, sum / (float)pool);
+    }
+}
+
 }  // namespace
 
 // proj: [rows, >= (H + G) * d + G * dv] with row stride proj_stride (elements); q_out: [rows, H * d] with row
@@ -122,6 +160,29 @@ TB_EXPORT int tb_rope_norm_cache(const void* proj, int64_t proj_stride, void* q_
                                  (const __nv_bfloat16*)proj, proj_stride, (__nv_bfloat16*)q_out, q_stride,
                                  (__nv_bfloat16*)cache, positions, seq_of_row, block_table, bt_stride, inv_freq, g,
                                  write_kv);
+    else
+        return TB_ERR_BAD_DTYPE;
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+// cache: the layer's pages of keys and values ([G][page_size][d] keys then [G][page_size][dv] values a page), already
+// holding the step's rows; pool_cache: its pages of averaged blocks, same layout, entry b of a request's pooled pages
+// being block b; pool_table: the requests' tables of those pages.
+TB_EXPORT int tb_pool_blocks(const void* cache, void* pool_cache, const int* positions, const int* seq_of_row,
+                             const int* block_table, int bt_stride, const int* pool_table, int pool_bt_stride, int rows,
+                             int kv_heads, int dim, int vdim, int page_size, int pool, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (kv_heads < 1 || kv_heads > 65535 || dim < 1 || vdim < 1 || page_size < 1 || pool < 1) return TB_ERR_BAD_SIZE;
+    const dim3 grid(rows, kv_heads);
+    cudaError_t launched;
+    if (dtype == TB_F32)
+        launched = tb_launch_pdl(pool_blocks_kernel<float>, grid, dim3(128), (size_t)0, stream, (const float*)cache,
+                                 (float*)pool_cache, positions, seq_of_row, block_table, bt_stride, pool_table,
+                                 pool_bt_stride, kv_heads, dim, vdim, page_size, pool);
+    else if (dtype == TB_BF16)
+        launched = tb_launch_pdl(pool_blocks_kernel<__nv_bfloat16>, grid, dim3(128), (size_t)0, stream,
+                                 (const __nv_bfloat16*)cache, (__nv_bfloat16*)pool_cache, positions, seq_of_row,
+                                 block_table, bt_stride, pool_table, pool_bt_stride, kv_heads, dim, vdim, page_size, pool);
     else
         return TB_ERR_BAD_DTYPE;
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;

@@ -43,6 +43,8 @@ def graph_safe(model) -> bool:
         parts += [block.mixer, *block.norms.values()] + ([block.feed_forward] if block.feed_forward is not None else [])
         if getattr(block, "token_input", None) is not None:
             parts.append(block.token_input)
+        if getattr(block, "gates", None) is not None:
+            parts.append(block.gates)
     return all(getattr(part, "graph_safe", False) for part in parts)
 
 

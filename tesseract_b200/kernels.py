@@ -806,20 +806,24 @@ def conv_rope_cache(proj: torch.Tensor, taps: torch.Tensor, state: Optional[torc
                                         _i32(_code(proj.dtype)), _stream()), "conv_state_update")
 
 
-MASK_CAUSAL, MASK_WINDOW, MASK_BLOCKS = 0, 1, 2
+MASK_CAUSAL, MASK_WINDOW, MASK_BLOCKS, MASK_WINDOW_POOLED = 0, 1, 2, 3
 
 
 def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, cache: torch.Tensor,
                      positions: torch.Tensor, seq_of_row: torch.Tensor, block_table: torch.Tensor, *, heads: int,
                      kv_heads: int, dim: int, vdim: int, page_size: int, mask_kind: int, mask_size: int, sink: bool,
-                     scale: float, keys_per_value: int = 1) -> torch.Tensor:
+                     scale: float, keys_per_value: int = 1, sinks: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                     pooled=None) -> torch.Tensor:
     """Paged attention with 32-bit scores and weights: ``q`` ``[T, heads * dim]``, optional ``gate``
     ``[T, heads * vdim]`` (the output is multiplied by its sigmoid), ``out`` ``[T, heads * vdim]`` in the dtype of ``q``
     or in float32 (the weighted sums as they are, unrounded); pages hold ``[kv_heads, page_size, dim]`` keys then
     ``[kv_heads / keys_per_value, page_size, vdim]`` values, key head ``g`` reading value head ``g // keys_per_value``;
     ``keys_per_value = 0``: pages hold keys only and a key's first ``vdim`` numbers are its value.  ``mask_kind``:
-    causal, window or blocks of ``mask_size`` positions; ``sink``: one more entry of score 0 in the softmax's
-    denominator."""
+    causal, window or blocks of ``mask_size`` positions, or ``MASK_WINDOW_POOLED``: a window and, in front of it, one
+    averaged key and value per block of ``pool`` positions that lies wholly before the window, from
+    ``pooled = (pages of the averages, their block table, pool)``; ``sink``: one more entry of score 0 in the softmax's
+    denominator, or, with ``sinks`` (float32 ``[heads]``), of a learned score per head; ``softcap`` > 0: a score ``s``
+    becomes ``softcap * tanh(s / softcap)``."""
     _cuda(q, gate, out, cache, positions, seq_of_row, block_table)
     rows = q.shape[0]
     _need(q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_masked q")
@@ -830,6 +834,17 @@ def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_masked cache")
     if gate is not None:
         _need(gate.stride(1) == 1 and gate.shape == (rows, heads * vdim) and gate.dtype == q.dtype, "attention_masked gate")
+    if sinks is not None:
+        _cuda(sinks)
+        _need(sinks.dtype == torch.float32 and sinks.numel() == heads and sinks.is_contiguous(), "attention_masked sinks")
+    pool_cache = pool_table = None
+    pool = 0
+    if mask_kind == MASK_WINDOW_POOLED:
+        _need(pooled is not None and keys_per_value == 1, "attention_masked: a pooled window needs the pooled pages")
+        pool_cache, pool_table, pool = pooled
+        _cuda(pool_cache, pool_table)
+        _need(pool_cache.dtype == q.dtype and pool_cache.is_contiguous() and pool_table.dtype == torch.int32
+              and pool_table.stride(1) == 1 and pool >= 1, "attention_masked pooled pages")
     lib = load_library("attention_masked")
     _check(lib.tb_attention_masked(_ptr(q), _i64(q.stride(0)), _ptr(gate), _i64(gate.stride(0) if gate is not None else 0),
                                    _ptr(out), _i64(out.stride(0)), _ptr(cache), _ptr(positions), _ptr(seq_of_row),
@@ -837,6 +852,8 @@ def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
                                    _i32(kv_heads), _i32(dim), _i32(vdim), _i32(page_size), _i32(mask_kind),
                                    _i32(mask_size), _i32(1 if sink else 0), _f32(scale), _i32(keys_per_value),
                                    _i32(1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0),
+                                   _ptr(sinks), _f32(softcap), _ptr(pool_cache), _ptr(pool_table),
+                                   _i32(pool_table.stride(0) if pool_table is not None else 0), _i32(pool),
                                    _i32(_code(q.dtype)), _stream()), "attention_masked")
     return out
 
@@ -1021,6 +1038,48 @@ def add_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return a
 
 
+def blend_rows(a: torch.Tensor, b: torch.Tensor, x: float, y: float) -> torch.Tensor:
+    """``a = x * a + y * b`` in place (contiguous float32 tensors of one shape)."""
+    _cuda(a, b)
+    _need(a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous()
+          and a.shape == b.shape, "blend_rows takes two contiguous float32 tensors of one shape")
+    lib = load_library("pointwise")
+    _check(lib.tb_blend_rows(_ptr(a), _ptr(b), _i64(a.numel()), _f32(x), _f32(y), _stream()), "blend_rows")
+    return a
+
+
+def sigmoid_mul(a: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = a * sigmoid(gate)`` (``out`` may be ``a``), the arithmetic in 32-bit."""
+    _cuda(a, gate, out)
+    _need(a.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1 and a.shape == gate.shape == out.shape
+          and a.dtype == gate.dtype == out.dtype, "sigmoid_mul a/gate/out")
+    lib = load_library("pointwise")
+    _check(lib.tb_sigmoid_mul(_ptr(a), _i64(a.stride(0)), _ptr(gate), _i64(gate.stride(0)), _ptr(out), _i64(out.stride(0)),
+                              _i32(a.shape[0]), _i32(a.shape[1]), _i32(_code(a.dtype)), _stream()), "sigmoid_mul")
+    return out
+
+
+def gated_add_norm(residual: torch.Tensor, update: torch.Tensor, gate: torch.Tensor, gate_bias: torch.Tensor,
+                   scale: torch.Tensor, weight: Optional[torch.Tensor], out: Optional[torch.Tensor], eps: float) -> None:
+    """``residual += update * scale * sigmoid(gate + gate_bias)`` in 32-bit, in place, and, with ``weight`` and ``out``,
+    ``out = residual / sqrt(mean(residual^2) + eps) * weight`` (rounded once to the dtype of ``out``).  ``residual``,
+    ``update`` and ``gate`` are contiguous float32 ``[T, width]``; ``gate_bias``, ``scale`` and ``weight`` float32
+    ``[width]``."""
+    _cuda(residual, update, gate, gate_bias, scale, weight, out)
+    rows, width = residual.shape
+    for t, what in ((residual, "residual"), (update, "update"), (gate, "gate")):
+        _f32_rows(t, (rows, width), f"gated_add_norm {what} is contiguous float32")
+    for t in (gate_bias, scale) + ((weight,) if weight is not None else ()):
+        _need(t.dtype == torch.float32 and t.numel() == width and t.is_contiguous(), "gated_add_norm vectors")
+    _need((weight is None) == (out is None), "gated_add_norm: a norm needs its weight and its output")
+    if out is not None:
+        _need(out.is_contiguous() and tuple(out.shape) == (rows, width), "gated_add_norm out")
+    lib = load_library("gated_residual")
+    _check(lib.tb_gated_add_norm(_ptr(residual), _ptr(update), _ptr(gate), _ptr(gate_bias), _ptr(scale), _ptr(weight),
+                                 _ptr(out), _i32(rows), _i32(width), _f32(eps),
+                                 _i32(_code(out.dtype if out is not None else torch.float32)), _stream()), "gated_add_norm")
+
+
 def embedding_scaled(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, factor: float) -> torch.Tensor:
     """``out[t] = float32(table[tokens[t]]) * factor`` for a float32 ``out``."""
     _cuda(tokens, table, out)
@@ -1060,6 +1119,24 @@ def rope_norm_cache(proj: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor
                                   _i32(1 if write_kv else 0), _i32(_code(proj.dtype)), _stream()), "rope_norm_cache")
 
 
+def pool_blocks(cache: torch.Tensor, pool_cache: torch.Tensor, positions: torch.Tensor, seq_of_row: torch.Tensor,
+                block_table: torch.Tensor, pool_table: torch.Tensor, *, kv_heads: int, dim: int, vdim: int, page_size: int,
+                pool: int) -> None:
+    """For every row whose position ends a block of ``pool`` positions: the block's averaged key and value, from the
+    pages of ``cache`` as they stand (the step's rows already written), into entry ``position // pool`` of the request's
+    pages of ``pool_cache`` (same page layout, addressed through ``pool_table``)."""
+    _cuda(cache, pool_cache, positions, seq_of_row, block_table, pool_table)
+    _need(cache.dtype == pool_cache.dtype and cache.is_contiguous() and pool_cache.is_contiguous(), "pool_blocks pages")
+    for t in (positions, seq_of_row, block_table, pool_table):
+        _need(t.dtype == torch.int32, "pool_blocks metadata must be int32")
+    _need(block_table.stride(1) == 1 and pool_table.stride(1) == 1, "pool_blocks tables")
+    lib = load_library("rope_norm_cache")
+    _check(lib.tb_pool_blocks(_ptr(cache), _ptr(pool_cache), _ptr(positions), _ptr(seq_of_row), _ptr(block_table),
+                              _i32(block_table.stride(0)), _ptr(pool_table), _i32(pool_table.stride(0)),
+                              _i32(positions.numel()), _i32(kv_heads), _i32(dim), _i32(vdim), _i32(page_size), _i32(pool),
+                              _i32(_code(cache.dtype)), _stream()), "pool_blocks")
+
+
 # ----------------------------------------------------------------------------- routed experts
 
 EXPERT_PLAIN, EXPERT_SQUARED_RELU = 0, 1
@@ -1077,6 +1154,23 @@ def choose_topk(logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) 
     lib = load_library("experts")
     _check(lib.tb_choose_topk(_ptr(logits), _ptr(ids), _ptr(weights), _i32(rows), _i32(experts), _i32(top), _stream()),
            "choose_topk")
+
+
+def choose_grouped(logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, *, groups: int, keep: int,
+                   weight_scale: float) -> None:
+    """Scores are the softmax over all of a row's ``logits`` (float32 ``[T, E]``).  The experts form ``groups`` equal runs
+    of neighbours; only experts of the ``keep`` groups with the largest best score can be chosen; of those the ``top``
+    largest scores (largest first, the lowest index among equals) go into ``ids``, and into ``weights`` their scores
+    over the chosen scores' sum, times ``weight_scale``."""
+    _cuda(logits, ids, weights)
+    rows, experts = logits.shape
+    top = ids.shape[1]
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "choose_grouped logits")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()
+          and tuple(ids.shape) == (rows, top) and tuple(weights.shape) == (rows, top), "choose_grouped ids/weights")
+    lib = load_library("experts")
+    _check(lib.tb_choose_grouped(_ptr(logits), _ptr(ids), _ptr(weights), _i32(rows), _i32(experts), _i32(top), _i32(groups),
+                                 _i32(keep), _f32(weight_scale), _stream()), "choose_grouped")
 
 
 def expert_plan(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor) -> None:
@@ -1209,9 +1303,10 @@ def token_gate(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, offse
 
 
 def lightning(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_start: torch.Tensor,
-              state_slots: torch.Tensor, *, num_seqs: int, heads: int, dim: int, vdim: int, max_new: int) -> torch.Tensor:
+              state_slots: torch.Tensor, *, num_seqs: int, heads: int, dim: int, vdim: int, max_new: int,
+              activation: bool = True) -> torch.Tensor:
     """``S_t = decay_h S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` per head with ``q, k, v = silu`` of the columns
-    ``[heads * dim | heads * dim | heads * vdim]`` of ``proj``; ``state`` float32 ``[slots, heads, dim, vdim]`` is read and
+    ``[heads * dim | heads * dim | heads * vdim]`` of ``proj`` (``activation`` False: the columns as they are); ``state`` float32 ``[slots, heads, dim, vdim]`` is read and
     renewed per sequence; ``out`` float32 ``[T, heads * vdim]``."""
     _cuda(proj, decay, state, out, row_start, state_slots)
     rows = out.shape[0]
@@ -1228,10 +1323,51 @@ def lightning(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out:
     _check(lib.tb_lightning(_ptr(proj), _i64(proj.stride(0)), _i32(0), _i32(heads * dim), _i32(2 * heads * dim), _ptr(decay),
                             _ptr(state), _ptr(out), _ptr(row_start), _ptr(state_slots), _i32(rows), _i32(num_seqs),
                             _i32(heads), _i32(dim), _i32(vdim), _i32(max(1, max_new)), _ptr(scratch),
-                            _i32(_code(proj.dtype)), _stream()), "lightning")
+                            _i32(1 if activation else 0), _i32(_code(proj.dtype)), _stream()), "lightning")
     if tiles:
         global launch_count
         launch_count += 2          # (the tiles' sums and the scan in front of the outputs)
+    return out
+
+
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def retention_prepare(proj: torch.Tensor, out: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], *,
+                      heads: int, dim: int, vdim: int, rot_dims: int, amplitude: float, k_scale: float) -> torch.Tensor:
+    """The columns ``[heads * dim q | heads * dim k | heads * vdim v]`` of ``proj`` widened into ``out`` (float32
+    ``[T, heads * (2 dim + vdim)]``): of every q and k head's first ``rot_dims`` numbers, number ``i`` and number
+    ``i + rot_dims / 2`` turn by ``position * inv_freq[i]`` (cosine and sine times ``amplitude``), k is multiplied by
+    ``k_scale`` afterwards, v is copied."""
+    _cuda(proj, out, positions, inv_freq)
+    rows = out.shape[0]
+    _need(proj.stride(1) == 1 and proj.shape[0] == rows and proj.shape[1] >= heads * (2 * dim + vdim), "retention_prepare proj")
+    _f32_rows(out, (rows, heads * (2 * dim + vdim)), "retention_prepare out is contiguous float32")
+    _need(positions.dtype == torch.int32, "retention_prepare positions must be int32")
+    if rot_dims:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2
+              and inv_freq.is_contiguous(), "retention_prepare inv_freq")
+    lib = load_library("lightning")
+    _check(lib.tb_retention_prepare(_ptr(proj), _i64(proj.stride(0)), _i32(0), _i32(heads * dim), _i32(2 * heads * dim),
+                                    _ptr(out), _ptr(positions), _ptr(inv_freq), _i32(rows), _i32(heads), _i32(dim),
+                                    _i32(vdim), _i32(rot_dims), _f32(amplitude), _f32(k_scale), _i32(_code(proj.dtype)),
+                                    _stream()), "retention_prepare")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, *, heads: int, vdim: int, eps: float,
+                   gate_kind: int) -> torch.Tensor:
+    """``out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * act(gate[t, h, :])`` with ``o`` float32
+    ``[T, heads * vdim]`` and ``act`` the sigmoid (``GATE_SIGMOID``) or SiLU (``GATE_SILU``)."""
+    _cuda(o, gate, out)
+    rows = o.shape[0]
+    _f32_rows(o, (rows, heads * vdim), "head_norm_gate o is contiguous float32")
+    _need(gate.stride(1) == 1 and gate.shape == (rows, heads * vdim) and out.stride(1) == 1
+          and out.shape == (rows, heads * vdim) and out.dtype == gate.dtype, "head_norm_gate gate/out")
+    lib = load_library("lightning")
+    _check(lib.tb_head_norm_gate(_ptr(o), _ptr(gate), _i64(gate.stride(0)), _ptr(out), _i64(out.stride(0)), _i32(rows),
+                                 _i32(heads), _i32(vdim), _f32(eps), _i32(gate_kind), _i32(_code(out.dtype)), _stream()),
+           "head_norm_gate")
     return out
 
 
@@ -1288,7 +1424,7 @@ def differential_combine(maps: torch.Tensor, gate: Optional[torch.Tensor], out: 
 def latent_rope_cache(down: torch.Tensor, q: torch.Tensor, q_full: torch.Tensor, cache: torch.Tensor,
                       weight: torch.Tensor, positions: torch.Tensor, seq_of_row: torch.Tensor, block_table: torch.Tensor,
                       inv_freq: Optional[torch.Tensor], *, heads: int, dim: int, rank: int, rot_width: int,
-                      rot_dims: int, page_size: int, eps: float) -> None:
+                      rot_dims: int, page_size: int, eps: float, amplitude: float = 1.0) -> None:
     """``down`` float32 ``[T, rank + rot_width]``: the first ``rank`` numbers over their root mean square times
     ``weight`` and the rotated rest go into the row's page (``[page, rank + rot_width]`` a page); the rotated parts of the
     query heads (``q`` ``[T, heads * (dim + rot_width)]``) go into ``q_full`` ``[T, heads * (rank + rot_width)]`` behind
@@ -1312,7 +1448,7 @@ def latent_rope_cache(down: torch.Tensor, q: torch.Tensor, q_full: torch.Tensor,
                                     _i64(q_full.stride(0)), _ptr(cache), _ptr(weight), _ptr(positions), _ptr(seq_of_row),
                                     _ptr(block_table), _i32(block_table.stride(0)), _ptr(inv_freq), _i32(rows), _i32(heads),
                                     _i32(dim), _i32(rank), _i32(rot_width), _i32(rot_dims), _i32(page_size), _f32(eps),
-                                    _i32(_code(q.dtype)), _stream()), "latent_rope_cache")
+                                    _f32(amplitude), _i32(_code(q.dtype)), _stream()), "latent_rope_cache")
 
 
 def attention_latent_mma_supported(dtype: torch.dtype, dim: int, vdim: int) -> bool:

@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS, TOKEN_INPUTS, Block, CacheBinding, DeferredNorm,
+from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS, RESIDUAL_GATES, TOKEN_INPUTS, Block, CacheBinding, DeferredNorm,
                      ResidualStream, Runtime, StepContext)
 from ..weights.loader import ExpectedTensor
 
@@ -39,6 +39,10 @@ def _part_specs(spec: ModelSpec):
             if not block_cls.accepts_token_input:
                 raise ValueError(f"block '{layer.block}' takes no token input")
             yield TOKEN_INPUTS, layer.token_input
+        if layer.residual_gates is not None:
+            if not block_cls.accepts_residual_gates:
+                raise ValueError(f"block '{layer.block}' takes no residual gates")
+            yield RESIDUAL_GATES, layer.residual_gates
     for injection in spec.injections:
         yield INJECTIONS, injection
     yield NORMS, spec.final_norm
@@ -87,10 +91,12 @@ class DecoderModel:
             norms = {role: build(NORMS, part) for role, part in layer.norms.items()}
             mixer = build(MIXERS, layer.mixer)
             feed_forward = build(FEED_FORWARDS, layer.feed_forward) if layer.feed_forward is not None else None
+            extras = {}
             if layer.token_input is not None:
-                self.layers.append(block_cls(norms, mixer, feed_forward, token_input=build(TOKEN_INPUTS, layer.token_input)))
-            else:
-                self.layers.append(block_cls(norms, mixer, feed_forward))
+                extras["token_input"] = build(TOKEN_INPUTS, layer.token_input)
+            if layer.residual_gates is not None:
+                extras["residual_gates"] = build(RESIDUAL_GATES, layer.residual_gates)
+            self.layers.append(block_cls(norms, mixer, feed_forward, **extras))
         self.injections = [build(INJECTIONS, part) for part in spec.injections]
         self.final_norm = build(NORMS, spec.final_norm)
         # A head that names the embedding's checkpoint tensor (tied embeddings) gets the same host tensor, and the

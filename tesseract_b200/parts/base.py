@@ -129,9 +129,23 @@ class PagedNeed:
 
     window: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    # positions that share one entry of a page (1: an entry per token; a need that keeps one entry per block of P
+    # positions says P: its pages fill P times as slowly and its pool is that much smaller)
+    positions_per_entry: int = 1
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         raise NotImplementedError
+
+    def entries_for(self, tokens: int) -> int:
+        """Entries that ``tokens`` positions fill or have begun to fill."""
+        return -(-tokens // self.positions_per_entry)
+
+    def pool_pages(self, token_pages: int, max_requests: int) -> int:
+        """Pages of this need's pool beside ``token_pages`` pages of a need with an entry per token: every request's
+        last page may be partly filled."""
+        if self.positions_per_entry == 1:
+            return token_pages
+        return -(-token_pages // self.positions_per_entry) + max_requests
 
     def first_needed_position(self, next_position: int) -> int:
         """The lowest position that a query at ``next_position`` or later can still read: pages wholly below it go
@@ -175,6 +189,10 @@ class PagedKeyValueNeed(PagedNeed):
     block: Optional[int] = None
     # value heads, where they are fewer than key heads (several score maps over one set of values); None: as many
     num_value_heads: Optional[int] = None
+    # with a window: the positions are also cut into consecutive runs of ``hold`` from 0, and the tokens of the run that
+    # is still being filled stay although the window has passed them (a later step reads them once more, to average
+    # the finished run, say)
+    hold: Optional[int] = None
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         value_heads = self.num_kv_heads if self.num_value_heads is None else self.num_value_heads
@@ -184,12 +202,41 @@ class PagedKeyValueNeed(PagedNeed):
         first = PagedNeed.first_needed_position(self, next_position)
         if self.block:
             first = max(first, (next_position // self.block) * self.block)
+        if self.hold and self.window:
+            first = min(first, (next_position // self.hold) * self.hold)
         return first
 
     def live_span(self) -> Optional[int]:
-        spans = [s for s in (self.window - 1 if self.window else None, self.block - 1 if self.block else None)
-                 if s is not None]
+        window = self.window - 1 if self.window else None
+        if window is not None and self.hold:
+            window = max(window, self.hold - 1)
+        spans = [s for s in (window, self.block - 1 if self.block else None) if s is not None]
         return min(spans) if spans else None
+
+
+@dataclass(frozen=True)
+class PooledBlocksNeed(PagedNeed):
+    """One key and one value per kv head for every block of ``pool`` positions (their averages, say): entry ``b`` of a
+    request's pages belongs to the positions ``b * pool .. b * pool + pool - 1``.  A page is laid out like a page of
+    :class:`PagedKeyValueNeed`; nothing is given back while the request lives."""
+
+    num_kv_heads: int = 1
+    key_dim: int = 0
+    value_dim: int = 0
+    pool: int = 1
+
+    @property
+    def positions_per_entry(self) -> int:
+        return self.pool
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (page_size * self.num_kv_heads * (self.key_dim + self.value_dim),)
+
+    def first_needed_position(self, next_position: int) -> int:
+        return 0
+
+    def live_span(self) -> Optional[int]:
+        return None
 
 
 @dataclass(frozen=True)
@@ -448,6 +495,21 @@ class TokenInput(Part):
         raise NotImplementedError
 
 
+class ResidualGates(Part):
+    """What weights a sublayer's result before it joins the stream, for a block that takes one: per sublayer
+    (``"mixer"``, ``"feed_forward"``) ``logits(which, rows_in)`` (float32 ``[T, hidden]`` from the sublayer's input rows),
+    ``bias(which)`` and ``scale(which)`` (float32 ``[hidden]``)."""
+
+    def logits(self, which: str, rows_in: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def bias(self, which: str) -> torch.Tensor:
+        raise NotImplementedError
+
+    def scale(self, which: str) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Head(Part):
     accepts_deferred_norm = False
 
@@ -463,6 +525,8 @@ class Block:
 
     # True if the constructor takes ``token_input`` (a :class:`TokenInput` that runs behind the sublayers)
     accepts_token_input = False
+    # True if the constructor takes ``residual_gates`` (a :class:`ResidualGates`)
+    accepts_residual_gates = False
 
     def __init__(self, norms: Mapping[str, Norm], mixer: Mixer, feed_forward: Optional[FeedForward]):
         self.norms = dict(norms)
@@ -491,3 +555,4 @@ EMBEDDINGS: Registry[Embedding] = Registry("embedding")
 HEADS: Registry[Head] = Registry("head")
 INJECTIONS: Registry[Injection] = Registry("injection")
 TOKEN_INPUTS: Registry[TokenInput] = Registry("token input")
+RESIDUAL_GATES: Registry[ResidualGates] = Registry("residual gates")

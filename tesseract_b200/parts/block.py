@@ -31,6 +31,15 @@ sum and both norms are one kernel.  A layer without a feed-forward leaves (x, a)
 
 The norm of a sublayer's result, the addition and the norm in front of the next sublayer are one kernel
 (``norm_add_norm``); it also leaves the rounded stream that the token input's first product reads.
+
+``gated_pre_norm`` is the pre-norm arrangement over a 32-bit stream in which every sublayer's result is weighted, feature
+by feature, by a learned scale and by a gate that reads the sublayer's own input:
+
+    h  = input_norm(x);       x <- x + mixer(h) * scale_1 * sigmoid(G_1 h + b_1)
+    m  = post_mixer_norm(x);  x <- x + feed_forward(m) * scale_2 * sigmoid(G_2 m + b_2)       (absent without one)
+
+The weighting, the addition and the norm in front of the next sublayer (the next block's first norm, or the final norm)
+are one kernel (``gated_add_norm``); the gate's product leaves 32-bit logits.
 """
 
 from __future__ import annotations
@@ -174,4 +183,82 @@ class SandwichBlock(Block):
         kernels.norm_add_norm(residual, update, post.norm_parameters(), None, None, copy, self.eps)
         if self.token_input is not None:
             self.token_input.forward(residual, ctx, rounded=copy if wants_copy else residual)
+        return ResidualStream(residual, None)
+
+
+class FinishedNorm(DeferredNorm):
+    """``norm(residual)`` that the block in front has already computed together with its last addition: ``residual``
+    is complete and ``materialize()`` hands out the rows."""
+
+    def __init__(self, norm: Norm, residual, rows):
+        super().__init__(norm, residual, None)
+        self._value = rows
+        self.done = True
+
+
+@BLOCKS.register("gated_pre_norm")
+class GatedPreNormBlock(Block):
+    """Norm roles ``input`` and, with a feed-forward, ``post_mixer``: RMS norms over the whole row of a 32-bit stream
+    that offer ``shared_statistic()`` (weight and eps).  ``extras``: per sublayer (``mixer``, ``feed_forward``) the
+    scale vector ``scale`` and the gate's ``Linear`` ``gate`` with its bias ``gate_bias``, built by the model from the
+    layer's ``residual_gates`` part."""
+
+    accepts_next_norm = True
+    accepts_residual_gates = True
+
+    def __init__(self, norms, mixer, feed_forward, residual_gates=None):
+        super().__init__(norms, mixer, feed_forward)
+        if residual_gates is None:
+            raise ValueError("a gated_pre_norm block needs its residual gates")
+        self.gates = residual_gates
+        for role, norm in self.norms.items():
+            if getattr(norm, "shared_statistic", lambda: None)() is None:
+                raise ValueError(f"a gated_pre_norm block takes RMS norms over the whole row; '{norm.kind}' ({role}) is not one")
+
+    @classmethod
+    def norm_roles(cls, with_feed_forward: bool = True) -> Tuple[str, ...]:
+        return ("input", "post_mixer") if with_feed_forward else ("input",)
+
+    def entry_norm(self) -> Optional[Norm]:
+        return self.norms["input"]
+
+    def _join(self, residual, update, rows_in, which: str, following: Optional[Norm]):
+        """``residual += update * scale * sigmoid(gate(rows_in))``; the rows of ``following`` over the new residual, or None."""
+        import torch
+
+        from .. import kernels
+
+        logits = self.gates.logits(which, rows_in)
+        statistic = getattr(following, "shared_statistic", lambda: None)() if following is not None else None
+        out = weight = None
+        eps = 0.0
+        if statistic is not None:
+            weight, eps = statistic
+            out = torch.empty(residual.shape, dtype=following.runtime.dtype, device=residual.device)
+        kernels.gated_add_norm(residual, update, logits, self.gates.bias(which), self.gates.scale(which), weight, out, eps)
+        return out
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: Optional[CacheBinding],
+                next_norm: Optional[Norm] = None) -> ResidualStream:
+        import torch
+
+        if stream.update_b is not None:
+            raise NotImplementedError("a gated_pre_norm block takes the stream as a residual and at most one pending update")
+        residual = stream.residual
+        if residual.dtype != torch.float32:
+            raise NotImplementedError("a gated_pre_norm block keeps its stream in 32-bit")
+        if stream.prepared is not None and stream.prepared.norm is self.norms["input"]:
+            h = stream.prepared.materialize()
+        else:
+            h = DeferredNorm(self.norms["input"], residual, stream.update).materialize()
+        mixed = self.mixer.forward(h, ctx, cache)
+        last = self.feed_forward is None
+        rows = self._join(residual, mixed, h, "mixer", next_norm if last else self.norms["post_mixer"])
+        if not last:
+            if rows is None:
+                rows = self.norms["post_mixer"].forward(residual)
+            update = self.feed_forward.forward(rows, ctx)
+            rows = self._join(residual, update, rows, "feed_forward", next_norm)
+        if rows is not None:
+            return ResidualStream(residual, None, prepared=FinishedNorm(next_norm, residual, rows))
         return ResidualStream(residual, None)

@@ -8,6 +8,12 @@ Per row ``h`` (the feed-forward's input):
 * the output is the weighted sum of the chosen experts' outputs, slots in order, plus, if the model has one, a
   shared expert of the same form (and a size of its own) that every row takes.
 
+Other routers and experts are a matter of parameters.  ``scoring`` ``"softmax_all"``: the scores are the softmax over
+all experts' logits; the experts form ``groups`` equal runs of neighbours, a group counts as much as its best score, and
+only experts of the ``keep_groups`` best groups can be chosen; the ``top_k`` largest scores among those are chosen and
+weighted by their scores over the chosen scores' sum (``+ 1e-20``), times ``weight_scale``.  ``expert_form``
+``"gated_silu"``: an expert (and the shared one) is ``down_e(silu(gate_e h) * (up_e h))``; gate and up are one product.
+
 The step's ``rows * top_k`` (row, slot) assignments are grouped by expert on the device; each of the experts' two
 products then runs as one launch over all groups, whose grid is sized for the worst case, so the host never learns
 (or waits for) how many rows an expert received and a step can be captured in a graph.  Router, assignment weights
@@ -30,8 +36,10 @@ from .linear import Linear
 @FEED_FORWARDS.register("routed_experts")
 class RoutedExperts(FeedForward):
     """params: ``hidden_size, num_experts, top_k, expert_size``, ``shared_size`` (None: no shared expert), optional
-    ``stream``; weights: ``router`` ``[experts, hidden]``, ``up.<e>`` ``[expert_size, hidden]`` and ``down.<e>``
-    ``[hidden, expert_size]`` for every expert ``e``, and with a shared expert ``shared_up``, ``shared_down``."""
+    ``stream``, ``scoring`` (``"softmax_chosen"`` | ``"softmax_all"``, the latter with ``groups``, ``keep_groups``,
+    ``weight_scale``), ``expert_form`` (``"squared_relu"`` | ``"gated_silu"``); weights: ``router`` ``[experts, hidden]``,
+    ``up.<e>`` ``[expert_size, hidden]`` and ``down.<e>`` ``[hidden, expert_size]`` for every expert ``e``, and with a
+    shared expert ``shared_up``, ``shared_down``; gated experts also ``gate.<e>`` and ``shared_gate``."""
 
     graph_safe = True
 
@@ -50,6 +58,24 @@ class RoutedExperts(FeedForward):
         # 32-bit accumulation, 32-bit logits; in a float32 run the package's own 32-bit product
         self.router = Linear(tensors["router"], runtime)
         experts = range(self.num_experts)
+        self.scoring = p.get("scoring") or "softmax_chosen"
+        self.form = p.get("expert_form") or "squared_relu"
+        if self.scoring not in ("softmax_chosen", "softmax_all") or self.form not in ("squared_relu", "gated_silu"):
+            raise ValueError("routed_experts: scoring is 'softmax_chosen' or 'softmax_all', expert_form 'squared_relu' or 'gated_silu'")
+        self.groups = int(p.get("groups") or 1)
+        self.keep_groups = int(p.get("keep_groups") or self.groups)
+        self.weight_scale = float(p.get("weight_scale") if p.get("weight_scale") is not None else 1.0)
+        if self.num_experts % self.groups or not 1 <= self.keep_groups <= self.groups \
+                or self.top_k > self.keep_groups * (self.num_experts // self.groups):
+            raise ValueError("routed_experts: groups must divide the experts, keep_groups lie between 1 and groups, and the "
+                             "kept groups hold at least top_k experts")
+        self.gated = self.form == "gated_silu"
+        if self.gated:      # an expert's gate rows, then its up rows: one product, then the gating
+            tensors = dict(tensors)
+            for e in experts:
+                tensors[f"up.{e}"] = torch.cat([tensors[f"gate.{e}"], tensors[f"up.{e}"]], dim=0)
+            if self.shared_size:
+                tensors["shared_up"] = torch.cat([tensors["shared_gate"], tensors["shared_up"]], dim=0)
         self.up = torch.stack([tensors[f"up.{e}"] for e in experts]).to(device=runtime.device, dtype=runtime.dtype).contiguous()
         self.down = torch.stack([tensors[f"down.{e}"] for e in experts]).to(device=runtime.device, dtype=runtime.dtype).contiguous()
         self.shared_up = self.shared_down = None
@@ -62,12 +88,17 @@ class RoutedExperts(FeedForward):
         p, w = spec.params, spec.weights
         hidden, size = int(p["hidden_size"]), int(p["expert_size"])
         out = {w["router"]: ExpectedTensor((int(p["num_experts"]), hidden))}
+        gated = p.get("expert_form") == "gated_silu"
         for e in range(int(p["num_experts"])):
             out[w[f"up.{e}"]] = ExpectedTensor((size, hidden))
             out[w[f"down.{e}"]] = ExpectedTensor((hidden, size))
+            if gated:
+                out[w[f"gate.{e}"]] = ExpectedTensor((size, hidden))
         if p.get("shared_size"):
             out[w["shared_up"]] = ExpectedTensor((int(p["shared_size"]), hidden))
             out[w["shared_down"]] = ExpectedTensor((hidden, int(p["shared_size"])))
+            if gated:
+                out[w["shared_gate"]] = ExpectedTensor((int(p["shared_size"]), hidden))
         return out
 
     @classmethod
@@ -89,7 +120,12 @@ class RoutedExperts(FeedForward):
         rows = x.shape[0]
         ids = torch.empty((rows, self.top_k), dtype=torch.int32, device=x.device)
         weights = torch.empty((rows, self.top_k), dtype=torch.float32, device=x.device)
-        kernels.choose_topk(self.router.forward(x, float32_out=True), ids, weights)
+        logits = self.router.forward(x, float32_out=True)
+        if self.scoring == "softmax_all":
+            kernels.choose_grouped(logits, ids, weights, groups=self.groups, keep=self.keep_groups,
+                                   weight_scale=self.weight_scale)
+        else:
+            kernels.choose_topk(logits, ids, weights)
         return ids, weights
 
     def forward(self, x, ctx: StepContext, follow=None):
@@ -101,15 +137,25 @@ class RoutedExperts(FeedForward):
         offsets = torch.empty(self.num_experts + 1, dtype=torch.int32, device=device)
         order = torch.empty(count, dtype=torch.int32, device=device)
         kernels.expert_plan(ids, self.num_experts, offsets, order)
-        hidden = torch.empty((count, self.expert_size), dtype=x.dtype, device=device)
-        kernels.expert_linear(x, self.up, hidden, offsets, order, source_div=self.top_k,
-                              epilogue=kernels.EXPERT_SQUARED_RELU)
+        if self.gated:
+            gate_up = torch.empty((count, 2 * self.expert_size), dtype=x.dtype, device=device)
+            kernels.expert_linear(x, self.up, gate_up, offsets, order, source_div=self.top_k)
+            hidden = torch.empty((count, self.expert_size), dtype=x.dtype, device=device)
+            kernels.gated_activation(gate_up, None, hidden, kernels.ACT_SILU)
+        else:
+            hidden = torch.empty((count, self.expert_size), dtype=x.dtype, device=device)
+            kernels.expert_linear(x, self.up, hidden, offsets, order, source_div=self.top_k,
+                                  epilogue=kernels.EXPERT_SQUARED_RELU)
         parts = torch.empty((count, self.hidden_size), dtype=torch.float32, device=device)
         kernels.expert_linear(hidden, self.down, parts, offsets, order, source_div=1)
         base = None
         if self.shared_size:
             z = self.shared_up.forward(x)
-            kernels.squared_relu(z, z)
+            if self.gated:
+                z = kernels.gated_activation(z, None, torch.empty((rows, self.shared_size), dtype=z.dtype, device=device),
+                                             kernels.ACT_SILU)
+            else:
+                kernels.squared_relu(z, z)
             base = self.shared_down.forward(z, float32_out=True)
         out = base if base is not None else torch.empty((rows, self.hidden_size), dtype=torch.float32, device=device)
         kernels.expert_combine(parts, weights, base, out)

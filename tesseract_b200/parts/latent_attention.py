@@ -36,7 +36,9 @@ _MASKS = {"causal": kernels.MASK_CAUSAL, "window": kernels.MASK_WINDOW}
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
     """params: ``hidden_size, num_heads, key_dim`` (plain)``, rot_width, value_dim, rank, scale, eps``, ``mask``, optional
-    ``stream``.  weights: ``q, down, down_norm, up_k, up_v, o``.  children: ``position`` (over ``rot_width``)."""
+    ``stream``, ``gate`` (bool: the concatenated heads are multiplied by ``sigmoid(Wg h)`` in front of the output
+    projection).  weights: ``q, down, down_norm, up_k, up_v, o`` and, with ``gate``, ``g``.  children: ``position`` (over
+    ``rot_width``; its ``amplitude``, if it has one, multiplies cosine and sine)."""
 
     graph_safe = True
 
@@ -63,7 +65,10 @@ class LatentAttention(Mixer):
         if not (1 <= self.entry <= 1024 and 1 <= self.rank <= 512):
             raise ValueError("the attention kernel takes a latent of up to 512 numbers and entries of up to 1024")
         H = self.num_heads
-        self.q_proj = Linear(tensors["q"], runtime)
+        self.gated = bool(p.get("gate"))
+        self.q_width = H * (self.key_dim + self.rot_width)
+        # (queries and the gate's pre-activations leave one product)
+        self.q_proj = Linear(torch.cat([tensors["q"], tensors["g"]], dim=0) if self.gated else tensors["q"], runtime)
         self.down_proj = Linear(tensors["down"], runtime)
         self.o_proj = Linear(tensors["o"], runtime)
         self.down_norm = runtime.vector_f32(tensors["down_norm"])
@@ -76,6 +81,7 @@ class LatentAttention(Mixer):
             raise ValueError(f"latent_attention rotates pairs or not at all, got position encoding '{self.position.kind}'")
         self.rot_dims = int(getattr(self.position, "dims", 0))
         self.inv_freq = getattr(self.position, "pair_inv_freq", None)
+        self.amplitude = float(getattr(self.position, "amplitude", 1.0))
         if self.rot_dims > self.rot_width:
             raise ValueError("the rotation covers more numbers than the rotated part has")
 
@@ -84,9 +90,12 @@ class LatentAttention(Mixer):
         p, w = spec.params, spec.weights
         hidden, heads, d, dr = int(p["hidden_size"]), int(p["num_heads"]), int(p["key_dim"]), int(p["rot_width"])
         dv, rank = int(p["value_dim"]), int(p["rank"])
-        return {w["q"]: ExpectedTensor((heads * (d + dr), hidden)), w["down"]: ExpectedTensor((rank + dr, hidden)),
-                w["down_norm"]: ExpectedTensor((rank,)), w["up_k"]: ExpectedTensor((heads * d, rank)),
-                w["up_v"]: ExpectedTensor((heads * dv, rank)), w["o"]: ExpectedTensor((hidden, heads * dv))}
+        out = {w["q"]: ExpectedTensor((heads * (d + dr), hidden)), w["down"]: ExpectedTensor((rank + dr, hidden)),
+               w["down_norm"]: ExpectedTensor((rank,)), w["up_k"]: ExpectedTensor((heads * d, rank)),
+               w["up_v"]: ExpectedTensor((heads * dv, rank)), w["o"]: ExpectedTensor((hidden, heads * dv))}
+        if p.get("gate"):
+            out[w["g"]] = ExpectedTensor((heads * dv, hidden))
+        return out
 
     @classmethod
     def random_tensor(cls, spec, role, shape, generator) -> torch.Tensor:
@@ -96,7 +105,7 @@ class LatentAttention(Mixer):
 
     def products(self):
         """``(name, Linear, epilogue)`` of the mixer's planned matrix products, for the printed kernel plan."""
-        return [("q", self.q_proj, plan.BF16), ("down", self.down_proj, plan.F32),
+        return [("q/gate" if self.gated else "q", self.q_proj, plan.BF16), ("down", self.down_proj, plan.F32),
                 ("o", self.o_proj, plan.F32 if self.stream_f32 else plan.BF16)]
 
     def attention_choice(self, rows: int) -> str:
@@ -124,13 +133,16 @@ class LatentAttention(Mixer):
         group = ctx.groups[cache.group]
         H, d, dr, rank, dv = self.num_heads, self.key_dim, self.rot_width, self.rank, self.value_dim
         q = self.q_proj.forward(x)
+        gate = None
+        if self.gated:
+            q, gate = q[:, :self.q_width], q[:, self.q_width:]
         down = self.down_proj.forward(x, float32_out=True)       # the latent's norm reads 32-bit numbers
         rows = q.shape[0]
         q_full = torch.empty((rows, H * self.entry), dtype=q.dtype, device=q.device)
         self._per_head(q.view(rows, H, d + dr)[:, :, :d], self.up_k_t, q_full.view(rows, H, self.entry)[:, :, :rank])
         kernels.latent_rope_cache(down, q, q_full, cache.storage, self.down_norm, ctx.positions, ctx.seq_of_row,
                                   group.block_table, self.inv_freq, heads=H, dim=d, rank=rank, rot_width=dr,
-                                  rot_dims=self.rot_dims, page_size=cache.page_size, eps=self.eps)
+                                  rot_dims=self.rot_dims, page_size=cache.page_size, eps=self.eps, amplitude=self.amplitude)
         mixed = torch.empty((rows, H * rank), dtype=q.dtype, device=q.device)
         if self.attention_choice(rows) == "attention_latent_mma":
             kernels.attention_latent_mma(q_full, mixed, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
@@ -143,4 +155,6 @@ class LatentAttention(Mixer):
                                      scale=self.scale, keys_per_value=0)
         out = torch.empty((rows, H * dv), dtype=q.dtype, device=q.device)
         self._per_head(mixed.view(rows, H, rank), self.up_v, out.view(rows, H, dv))
+        if gate is not None:
+            kernels.sigmoid_mul(out, gate, out)
         return self.o_proj.forward(out, float32_out=self.stream_f32)

@@ -121,6 +121,49 @@ class PolyNormMLP(FeedForward):
         return self.down_proj.forward(z, float32_out=self.stream_f32)
 
 
+@FEED_FORWARDS.register("plain_mlp")
+class PlainMLP(FeedForward):
+    """A dense feed-forward without a gate: ``down(act(up h))``, ``act`` the squared ReLU ``max(z, 0)^2``.
+
+    params: ``hidden_size, intermediate_size``, ``activation`` (``"squared_relu"``), optional ``stream``; weights:
+    ``up, down``.  The activation is a kernel of its own behind the first product; the down product comes out in 32-bit
+    for a residual stream kept in 32-bit."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.intermediate_size = int(p["intermediate_size"])
+        if p.get("activation") != "squared_relu":
+            raise ValueError(f"activation must be 'squared_relu', got {p.get('activation')!r}")
+        self.stream_f32 = p.get("stream") == "float32"
+        self.up_proj = Linear(tensors["up"], runtime)
+        self.down_proj = Linear(tensors["down"], runtime)
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
+        p, w = spec.params, spec.weights
+        hidden, inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        return {w["up"]: ExpectedTensor((inter, hidden)), w["down"]: ExpectedTensor((hidden, inter))}
+
+    @classmethod
+    def random_tensor(cls, spec, role, shape, generator) -> torch.Tensor:
+        return torch.randn(shape, generator=generator, dtype=torch.float32) * (shape[-1] ** -0.5)
+
+    def products(self):
+        """``(name, Linear, epilogue)`` of the feed-forward's matrix products, for the printed kernel plan."""
+        return [("up", self.up_proj, plan.BF16), ("down", self.down_proj, plan.F32 if self.stream_f32 else plan.BF16)]
+
+    def forward(self, x, ctx: StepContext, follow=None):
+        if isinstance(x, DeferredNorm):
+            x = x.materialize()
+        z = self.up_proj.forward(x)
+        kernels.squared_relu(z, z)
+        return self.down_proj.forward(z, float32_out=self.stream_f32)
+
+
 _ACTIVATIONS = {"silu": kernels.ACT_SILU, "gelu_tanh": kernels.ACT_GELU_TANH}
 
 

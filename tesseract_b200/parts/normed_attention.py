@@ -7,9 +7,15 @@ Per row ``h`` (the mixer's input):
 * the position encoding (``rotary_blend``, rotate-half layout) turns the first ``dims`` numbers of every query and
   key head; with ``qk_norm_eps`` every query and key head is then divided by ``sqrt(mean(head^2) + qk_norm_eps)``
   (no weight); rotated, normalised keys and the values go into the request's pages;
-* every row attends over the keys its mask lets it see: ``causal`` (all up to its own position) or ``window`` (its own
-  and the ``size - 1`` positions before it; older pages go back to the pool).  Scores ``(q . k) * scale``, the softmax
-  and the weights are 32-bit;
+* every row attends over the keys its mask lets it see: ``causal`` (all up to its own position), ``window`` (its own
+  and the ``size - 1`` positions before it; older pages go back to the pool) or ``window_pooled``: the window and, for
+  every block of ``pool`` positions that lies wholly in front of it (block ``b`` holds ``b * pool .. b * pool + pool - 1``
+  and is seen from position ``p`` if ``b * pool + pool - 1 <= p - size``), one key and one value that are the averages of
+  the block's keys and values as the pages hold them; tokens that have left the window and whose block is not yet seen
+  are not seen.  The averages live in pages of their own (an entry a block) and are written by the step that brings a
+  block's last token.  Scores ``(q . k) * scale``, with ``softcap`` then ``softcap * tanh(score / softcap)``, the softmax
+  and the weights are 32-bit; with ``sink`` the denominator also holds ``exp`` of a learned number per query head;
+* with ``bias`` the three projections add a bias each;
 * the output projection's result comes out in 32-bit for a residual stream kept in 32-bit (``stream`` = ``"float32"``).
 
 Rotation, normalisation and the cache write are one kernel; the attention kernel is the one the other mixers with
@@ -26,17 +32,19 @@ import torch
 from .. import kernels, plan
 from ..config.spec import PartSpec
 from ..weights.loader import ExpectedTensor
-from .base import MIXERS, POSITION_ENCODINGS, DeferredNorm, Mixer, PagedKeyValueNeed, Runtime, StepContext
+from .base import (MIXERS, POSITION_ENCODINGS, DeferredNorm, Mixer, PagedKeyValueNeed, PooledBlocksNeed, Runtime,
+                   StepContext)
 from .linear import Linear
 
-_MASKS = {"causal": kernels.MASK_CAUSAL, "window": kernels.MASK_WINDOW}
+_MASKS = {"causal": kernels.MASK_CAUSAL, "window": kernels.MASK_WINDOW, "window_pooled": kernels.MASK_WINDOW_POOLED}
 
 
 @MIXERS.register("normed_attention")
 class NormedAttention(Mixer):
     """params: ``hidden_size, num_heads, num_kv_heads, key_dim, value_dim, scale``, ``mask`` (``{"kind": "causal" |
-    "window", "size": n}``), ``qk_norm_eps`` (None: queries and keys stay as rotated), optional ``stream``.
-    weights: ``q, k, v, o``.  children: ``position``."""
+    "window" | "window_pooled", "size": n, "pool": P}``), ``qk_norm_eps`` (None: queries and keys stay as rotated),
+    optional ``softcap``, ``sink`` (bool), ``bias`` (bool), ``stream``.  weights: ``q, k, v, o``, with ``bias`` also
+    ``q_bias, k_bias, v_bias``, with ``sink`` also ``sink`` ``[num_heads]``.  children: ``position``."""
 
     graph_safe = True      # reads only device-side metadata of the step (and its shape)
 
@@ -54,8 +62,16 @@ class NormedAttention(Mixer):
             raise ValueError(f"mask kind must be one of {sorted(_MASKS)}, got {mask.get('kind')!r}")
         self.mask_kind = mask["kind"]
         self.mask_size = int(mask.get("size") or 0)
-        if self.mask_kind == "window" and self.mask_size < 1:
-            raise ValueError("a 'window' mask needs a positive size")
+        if self.mask_kind != "causal" and self.mask_size < 1:
+            raise ValueError(f"a '{self.mask_kind}' mask needs a positive size")
+        self.pool = int(mask.get("pool") or 0)
+        if self.mask_kind == "window_pooled" and self.pool < 1:
+            raise ValueError("a 'window_pooled' mask needs a positive pool")
+        self.softcap = float(p.get("softcap") or 0.0)
+        if self.softcap < 0.0:
+            raise ValueError("softcap must not be negative")
+        self.sinks = runtime.vector_f32(tensors["sink"]) if p.get("sink") else None
+        self.biased = bool(p.get("bias"))
         eps = p.get("qk_norm_eps")
         self.unit_norm = eps is not None
         self.qk_norm_eps = float(eps) if eps is not None else 0.0
@@ -66,7 +82,8 @@ class NormedAttention(Mixer):
             raise ValueError("the attention kernel takes keys of up to 1024 and values of up to 512 numbers a head")
         self.q_width = self.num_heads * self.key_dim
         self.o_width = self.num_heads * self.value_dim
-        self.in_proj = Linear(torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0), runtime)
+        bias = torch.cat([tensors["q_bias"], tensors["k_bias"], tensors["v_bias"]]) if self.biased else None
+        self.in_proj = Linear(torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0), runtime, bias=bias)
         self.o_proj = Linear(tensors["o"], runtime)
         position_spec = spec.children.get("position") or PartSpec.make("none")
         self.position = POSITION_ENCODINGS.get(position_spec.kind)(position_spec, {}, runtime)
@@ -83,15 +100,25 @@ class NormedAttention(Mixer):
         p, w = spec.params, spec.weights
         hidden, d, dv = int(p["hidden_size"]), int(p["key_dim"]), int(p["value_dim"])
         heads, kv = int(p["num_heads"]), int(p["num_kv_heads"])
-        return {
+        out = {
             w["q"]: ExpectedTensor((heads * d, hidden)),
             w["k"]: ExpectedTensor((kv * d, hidden)),
             w["v"]: ExpectedTensor((kv * dv, hidden)),
             w["o"]: ExpectedTensor((hidden, heads * dv)),
         }
+        if p.get("bias"):
+            out.update({w["q_bias"]: ExpectedTensor((heads * d,)), w["k_bias"]: ExpectedTensor((kv * d,)),
+                        w["v_bias"]: ExpectedTensor((kv * dv,))})
+        if p.get("sink"):
+            out[w["sink"]] = ExpectedTensor((heads,))
+        return out
 
     @classmethod
     def random_tensor(cls, spec, role, shape, generator) -> torch.Tensor:
+        if role.endswith("_bias"):
+            return torch.randn(shape, generator=generator, dtype=torch.float32) * 0.3
+        if role == "sink":
+            return torch.randn(shape, generator=generator, dtype=torch.float32)
         return torch.randn(shape, generator=generator, dtype=torch.float32) * (shape[-1] ** -0.5)
 
     def products(self):
@@ -101,12 +128,31 @@ class NormedAttention(Mixer):
         return [("q/k/v", self.in_proj, plan.BF16), ("o", self.o_proj, plan.F32 if self.stream_f32 else plan.BF16)]
 
     def cache_need(self):
+        if self.mask_kind == "window_pooled":
+            # the tokens of a block stay until the block is averaged, although the window may have passed them
+            return (PagedKeyValueNeed(num_kv_heads=self.num_kv_heads, key_dim=self.key_dim, value_dim=self.value_dim,
+                                      window=self.mask_size, hold=self.pool),
+                    PooledBlocksNeed(num_kv_heads=self.num_kv_heads, key_dim=self.key_dim, value_dim=self.value_dim,
+                                     pool=self.pool))
         return PagedKeyValueNeed(num_kv_heads=self.num_kv_heads, key_dim=self.key_dim, value_dim=self.value_dim,
                                  window=self.mask_size if self.mask_kind == "window" else None)
+
+    def attention_choice(self, rows: int) -> str:
+        """The attention kernel of a step of ``rows`` rows: the tensor-core kernels know neither a cap, a learned sink
+        nor pooled blocks."""
+        if self.softcap or self.sinks is not None or self.mask_kind == "window_pooled":
+            return "attention_masked"
+        return plan.masked_attention(self.runtime.dtype, rows, self.key_dim, self.value_dim,
+                                     heads_per_kv=self.num_heads // self.num_kv_heads)
 
     def forward(self, x, ctx: StepContext, cache):
         if isinstance(x, DeferredNorm):
             x = x.materialize()
+        pooled = None
+        if self.mask_kind == "window_pooled":
+            if not isinstance(cache, tuple) or len(cache) != 2:
+                raise RuntimeError("a pooled window needs two cache bindings: the tokens' pages and the blocks'")
+            cache, pooled = cache
         if cache is None or cache.storage is None:
             raise RuntimeError("normed_attention needs a paged key/value cache binding")
         if not cache.writes:
@@ -119,9 +165,15 @@ class NormedAttention(Mixer):
                                 amplitude=self.amplitude, heads=self.num_heads, kv_heads=self.num_kv_heads,
                                 dim=self.key_dim, vdim=self.value_dim, rot_dims=self.rot_dims,
                                 unit_norm=self.unit_norm, eps=self.qk_norm_eps, page_size=cache.page_size)
+        extras = {}
+        if pooled is not None:
+            pool_table = ctx.groups[pooled.group].block_table
+            kernels.pool_blocks(cache.storage, pooled.storage, ctx.positions, ctx.seq_of_row, group.block_table, pool_table,
+                                kv_heads=self.num_kv_heads, dim=self.key_dim, vdim=self.value_dim,
+                                page_size=cache.page_size, pool=self.pool)
+            extras["pooled"] = (pooled.storage, pool_table, self.pool)
         attended = torch.empty((rows, self.o_width), dtype=proj.dtype, device=proj.device)
-        choice = plan.masked_attention(proj.dtype, rows, self.key_dim, self.value_dim,
-                                       heads_per_kv=self.num_heads // self.num_kv_heads)
+        choice = self.attention_choice(rows)
         if choice == "attention_rows_mma":
             kernels.attention_rows_mma(q, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
                                        heads=self.num_heads, kv_heads=self.num_kv_heads, dim=self.key_dim,
@@ -136,5 +188,6 @@ class NormedAttention(Mixer):
             kernels.attention_masked(q, None, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
                                      heads=self.num_heads, kv_heads=self.num_kv_heads, dim=self.key_dim,
                                      vdim=self.value_dim, page_size=cache.page_size, mask_kind=_MASKS[self.mask_kind],
-                                     mask_size=self.mask_size, sink=False, scale=self.scale)
+                                     mask_size=self.mask_size, sink=False, scale=self.scale, sinks=self.sinks,
+                                     softcap=self.softcap, **extras)
         return self.o_proj.forward(attended, float32_out=self.stream_f32)

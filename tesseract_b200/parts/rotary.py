@@ -94,8 +94,10 @@ class RotaryPairs(PositionEncoding):
     """Rotation of neighbouring pairs: of every head's first ``dims`` numbers, numbers ``2i`` and ``2i + 1`` turn by
     ``position * base^(-2i / dims)``; the rest of the head passes unchanged.
 
-    params: ``head_dim``, ``dims`` (even, at most ``head_dim``), ``base``, optional ``scaling`` (mapping with ``factor``,
-    ``low``, ``high``, ``original``: :func:`banded_inverse_frequencies`).  The frequencies are taken in 64-bit on
+    params: ``head_dim``, ``dims`` (even, at most ``head_dim``), ``base``, optional ``scaling``: a mapping with ``factor``,
+    ``low``, ``high``, ``original`` (:func:`banded_inverse_frequencies`), or one with ``factor``, ``original``, ``fast``,
+    ``slow`` (:func:`blended_inverse_frequencies`, which also raises ``amplitude``, the factor on cosine and sine, above
+    1).  The frequencies are taken in 64-bit on
     the host and rounded once to 32-bit; the angle and its sine and cosine are 32-bit, in the kernel that applies
     them (the mixer's rotate-and-store kernel reads ``pair_inv_freq`` and ``dims``)."""
 
@@ -110,7 +112,14 @@ class RotaryPairs(PositionEncoding):
         if not self.base > 0.0:
             raise ValueError("the rotation's base must be positive")
         scaling = params.get("scaling")
-        self.inv_freq_host = banded_inverse_frequencies(self.dims, self.base, dict(scaling) if scaling else None).astype(np.float32)
+        self.amplitude = 1.0
+        if scaling and "fast" in dict(scaling):
+            if self.base == 1.0:
+                raise ValueError("blended frequencies need a base other than 1")
+            frequencies, self.amplitude = blended_inverse_frequencies(self.dims, self.base, dict(scaling))
+            self.inv_freq_host = frequencies.astype(np.float32)
+        else:
+            self.inv_freq_host = banded_inverse_frequencies(self.dims, self.base, dict(scaling) if scaling else None).astype(np.float32)
         self.pair_inv_freq = torch.from_numpy(self.inv_freq_host).to(runtime.device) if self.dims else None
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
