@@ -2,8 +2,9 @@
 
 ``forward(config, tensors, tokens)`` takes the dictionary of ``config.json``, a mapping from tensor name to a numpy
 array, and one sequence's token ids; it returns the logits of every position and the stream behind every layer.
-``store`` is applied wherever a serving path keeps numbers in the run dtype between two kernels whose order matters for
-a mechanism (cached keys and values in front of pooling); the default keeps float64.
+``store`` is applied wherever a serving path may keep numbers in 16 bits between two of its kernels (normed rows,
+projected rows, cached keys and values in front of pooling, what enters an output product); the default keeps float64,
+and ``bfloat16`` measures what such rounding alone does to a result.
 """
 
 from __future__ import annotations
@@ -15,6 +16,37 @@ import numpy as np
 
 def identity(x):
     return x
+
+
+def bfloat16(x):
+    """``x`` rounded to bfloat16 and widened again."""
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float64)).to(torch.bfloat16).to(torch.float64).numpy()
+
+
+def load_folder(folder):
+    """``(config, {name: float64 array})`` of a model folder, read with a parser of its own."""
+    import json
+    import os
+    import struct
+
+    import torch
+
+    with open(os.path.join(folder, "config.json")) as handle:
+        config = json.load(handle)
+    raw = open(os.path.join(folder, "model.safetensors"), "rb").read()
+    (size,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + size])
+    kinds = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16}
+    tensors = {}
+    for name, entry in header.items():
+        if name == "__metadata__":
+            continue
+        first, last = entry["data_offsets"]
+        flat = torch.frombuffer(bytearray(raw[8 + size + first:8 + size + last]), dtype=kinds[entry["dtype"]])
+        tensors[name] = flat.to(torch.float64).numpy().reshape(entry["shape"])
+    return config, tensors
 
 
 def sigmoid(z):
@@ -85,7 +117,7 @@ def latent_attention(m, w, h, eps, store=identity):
     positions = np.arange(T)
     rot = m.get("rot") or {"dims": 0, "base": 10000.0}
     freq, amp = stretched_frequencies(rot["dims"], rot["base"], rot.get("scaling")) if rot["dims"] else (np.zeros(0), 1.0)
-    q = (h @ w["q"].T).reshape(T, H, d + dr)
+    q = store(h @ w["q"].T).reshape(T, H, d + dr)
     down = h @ w["dkv"].T
     c = store(rms_norm(down[:, :rank], w["dkv.norm"], eps))
     k_rot = store(rotate(down[:, None, rank:], positions, freq, amp, "pairs"))[:, 0]          # [T, dr], one for all heads
@@ -98,7 +130,7 @@ def latent_attention(m, w, h, eps, store=identity):
             scores = (k_plain[:t + 1, head] @ q[t, head, :d] + k_rot[:t + 1] @ q_rot[t, head]) * m["scale"]
             weights = np.exp(scores - scores.max())
             out[t, head] = (weights / weights.sum()) @ v[:t + 1, head]
-    gated = out.reshape(T, H * dv) * sigmoid(h @ w["g"].T)
+    gated = store(out.reshape(T, H * dv) * sigmoid(store(h @ w["g"].T)))
     return gated @ w["o"].T
 
 
@@ -111,10 +143,10 @@ def pooled_window_attention(m, w, h, eps, store=identity):
     positions = np.arange(T)
     rot = m.get("rot") or {"dims": 0, "base": 10000.0}
     freq, amp = stretched_frequencies(rot["dims"], rot["base"], rot.get("scaling")) if rot["dims"] else (np.zeros(0), 1.0)
-    q = (h @ w["q"].T + w["q.b"]).reshape(T, H, d)
-    k = (h @ w["k"].T + w["k.b"]).reshape(T, G, d)
+    q = store(h @ w["q"].T + w["q.b"]).reshape(T, H, d)
+    k = store(h @ w["k"].T + w["k.b"]).reshape(T, G, d)
     v = store((h @ w["v"].T + w["v.b"]).reshape(T, G, dv))
-    q = rms_divide(rotate(q, positions, freq, amp, "halves"), eps)
+    q = store(rms_divide(rotate(q, positions, freq, amp, "halves"), eps))
     k = store(rms_divide(rotate(k, positions, freq, amp, "halves"), eps))
     blocks = T // P
     pooled_k = store(np.stack([k[b * P:(b + 1) * P].mean(axis=0) for b in range(blocks)]) if blocks else np.zeros((0, G, d)))
@@ -134,19 +166,19 @@ def pooled_window_attention(m, w, h, eps, store=identity):
             top = max(scores.max(), sink)
             weights = np.exp(scores - top)
             out[t, head] = (weights / (weights.sum() + math.exp(sink - top))) @ values
-    return out.reshape(T, H * dv) @ w["o"].T
+    return store(out.reshape(T, H * dv)) @ w["o"].T
 
 
-def retention(m, w, h, eps, state=None):
+def retention(m, w, h, eps, state=None, store=identity, first_position=0):
     """Linear attention with a fixed decay per head; returns ``(output, state behind the last row)``."""
     T = h.shape[0]
     H, d, dv = m["heads"], m["dim"], m["vdim"]
-    positions = np.arange(T)
+    positions = np.arange(T) + first_position
     rot = m.get("rot") or {"dims": 0, "base": 10000.0}
     freq, amp = stretched_frequencies(rot["dims"], rot["base"], rot.get("scaling")) if rot["dims"] else (np.zeros(0), 1.0)
-    q = rotate((h @ w["q"].T).reshape(T, H, d), positions, freq, amp, "halves")
-    k = rotate((h @ w["k"].T).reshape(T, H, d), positions, freq, amp, "halves") * d ** -0.5
-    v = (h @ w["v"].T).reshape(T, H, dv)
+    q = rotate(store(h @ w["q"].T).reshape(T, H, d), positions, freq, amp, "halves")
+    k = rotate(store(h @ w["k"].T).reshape(T, H, d), positions, freq, amp, "halves") * d ** -0.5
+    v = store(h @ w["v"].T).reshape(T, H, dv)
     S = np.zeros((H, d, dv)) if state is None else state.copy()
     out = np.zeros((T, H, dv))
     for t in range(T):
@@ -154,29 +186,31 @@ def retention(m, w, h, eps, state=None):
             S[head] = m["decay"][head] * S[head] + np.outer(k[t, head], v[t, head])
             out[t, head] = S[head].T @ q[t, head]
     normed = rms_divide(out, eps).reshape(T, H * dv)
-    return (normed * silu(h @ w["g"].T)) @ w["o"].T, S
+    return store(normed * silu(store(h @ w["g"].T))) @ w["o"].T, S
 
 
 def parallel_mixer(m, w, h, eps, store=identity):
     left = pooled_window_attention(m["left"], {k[5:]: a for k, a in w.items() if k.startswith("left.")}, h, eps, store)
-    right, _ = retention(m["right"], {k[6:]: a for k, a in w.items() if k.startswith("right.")}, h, eps)
+    right, _ = retention(m["right"], {k[6:]: a for k, a in w.items() if k.startswith("right.")}, h, eps, store=store)
     return m["left_scale"] * left + m["right_scale"] * right
 
 
 # ----------------------------------------------------------------------------- feed-forwards
 
 
-def dense_feed_forward(w, h):
-    z = np.maximum(h @ w["up"].T, 0.0)
-    return (z * z) @ w["down"].T
+def dense_feed_forward(w, h, store=identity):
+    z = np.maximum(store(h @ w["up"].T), 0.0)
+    return store(z * z) @ w["down"].T
 
 
-def gated_expert(w, prefix, h):
-    return (silu(h @ w[prefix + "gate"].T) * (h @ w[prefix + "up"].T)) @ w[prefix + "down"].T
+def gated_expert(w, prefix, h, store=identity):
+    return store(silu(store(h @ w[prefix + "gate"].T)) * store(h @ w[prefix + "up"].T)) @ w[prefix + "down"].T
 
 
-def route(mlp, logits):
-    """``(chosen experts, weights)`` of one row from its router logits."""
+def route(mlp, logits, gaps=None):
+    """``(chosen experts, weights)`` of one row from its router logits.  ``gaps`` (a list) receives how far, in scores,
+    the closest decision was from going the other way: the last kept group against the first one left out, and the last
+    chosen expert against the best one not chosen."""
     r = mlp["router"]
     experts, top = r["experts"], r["top"]
     scores = np.exp(logits - logits.max())
@@ -186,31 +220,42 @@ def route(mlp, logits):
     best = [scores[g * per:(g + 1) * per].max() for g in range(groups["count"])]
     kept = sorted(range(groups["count"]), key=lambda g: (-best[g], g))[:groups["keep"]]
     allowed = [e for e in range(experts) if e // per in kept]
-    chosen = sorted(allowed, key=lambda e: (-scores[e], e))[:top]
+    ranked = sorted(allowed, key=lambda e: (-scores[e], e))
+    chosen = ranked[:top]
+    if gaps is not None:
+        order = sorted(range(groups["count"]), key=lambda g: (-best[g], g))
+        if groups["keep"] < groups["count"]:
+            gaps.append(best[order[groups["keep"] - 1]] - best[order[groups["keep"]]])
+        if top < len(ranked):
+            gaps.append(scores[ranked[top - 1]] - scores[ranked[top]])
     weights = scores[chosen] / (scores[chosen].sum() + 1e-20) * r["scale"]
     return chosen, weights
 
 
-def expert_feed_forward(mlp, w, h):
+def expert_feed_forward(mlp, w, h, store=identity, close_calls=None):
+    """``close_calls`` (a dictionary) receives, per row, the smallest gap of its routing decisions (see :func:`route`)."""
     out = np.zeros((h.shape[0], w["e0.down"].shape[0]))
     logits = h @ w["router"].T
     for t in range(h.shape[0]):
-        chosen, weights = route(mlp, logits[t])
+        gaps = []
+        chosen, weights = route(mlp, logits[t], gaps)
+        if close_calls is not None and gaps:
+            close_calls[t] = min(close_calls.get(t, 1.0), min(gaps))
         for e, weight in zip(chosen, weights):
-            out[t] += weight * gated_expert(w, f"e{e}.", h[t:t + 1])[0]
+            out[t] += weight * gated_expert(w, f"e{e}.", h[t:t + 1], store)[0]
     if mlp.get("shared"):
-        out += gated_expert(w, "shared.", h)
+        out += gated_expert(w, "shared.", h, store)
     return out
 
 
 # ----------------------------------------------------------------------------- the model
 
 
-def layer_forward(config, tensors, index, x, store=identity):
+def layer_forward(config, tensors, index, x, store=identity, close_calls=None):
     layer, eps, prefix = config["layers"][index], config["norm"]["eps"], f"l{index}."
     w = {name[len(prefix):]: a for name, a in tensors.items() if name.startswith(prefix)}
     mix = {name[4:]: a for name, a in w.items() if name.startswith("mix.")}
-    h = rms_norm(x, w["norm1"], eps)
+    h = store(rms_norm(x, w["norm1"], eps))
     if layer["type"] == "latent_attention":
         mixed = latent_attention(layer["mixer"], mix, h, eps, store)
     elif layer["type"] == "parallel":
@@ -221,18 +266,19 @@ def layer_forward(config, tensors, index, x, store=identity):
     mlp = layer.get("mlp")
     if mlp is None:
         return x
-    h = rms_norm(x, w["norm2"], eps)
+    h = store(rms_norm(x, w["norm2"], eps))
     feed = {name[4:]: a for name, a in w.items() if name.startswith("mlp.")}
-    update = dense_feed_forward(feed, h) if mlp["kind"] == "dense" else expert_feed_forward(mlp, feed, h)
+    update = dense_feed_forward(feed, h, store) if mlp["kind"] == "dense" else expert_feed_forward(mlp, feed, h, store, close_calls)
     return x + update * w["ls2"] * sigmoid(h @ w["rg2"].T + w["rg2.b"])
 
 
-def forward(config, tensors, tokens, store=identity):
-    """``(logits [T, vocab], [stream behind layer 0, 1, ...])``."""
+def forward(config, tensors, tokens, store=identity, close_calls=None):
+    """``(logits [T, vocab], [stream behind layer 0, 1, ...])``.  ``close_calls`` (a dictionary) receives, per position, the
+    smallest gap by which a router of any layer decided."""
     x = tensors["embed"][np.asarray(tokens)] * config["embedding"]["scale"]
     streams = []
     for index in range(len(config["layers"])):
-        x = layer_forward(config, tensors, index, x, store)
+        x = layer_forward(config, tensors, index, x, store, close_calls)
         streams.append(x.copy())
-    logits = rms_norm(x, tensors["final.norm"], config["norm"]["eps"]) @ tensors["head"].T
+    logits = store(rms_norm(x, tensors["final.norm"], config["norm"]["eps"])) @ tensors["head"].T
     return logits, streams
