@@ -1,6 +1,7 @@
 // Paged attention on the tensor cores, for prompt portions and (second kernel) for steps of few rows, with 32-bit
 // scores and weights kept to 32-bit accuracy: the masks and page layout of attention_masked.cu (keys and values of separate widths; causal, sliding window or
-// blocks of positions), for bfloat16 queries, keys and values.
+// blocks of positions, or a window with averaged blocks in front of it, which are walked first, from pages of their
+// own), its learned sink per query head and its cap on the scores, for bfloat16 queries, keys and values.
 //
 //   S = Q K^T      mma.sync m16n8k16 on bfloat16 operands with 32-bit accumulators: the products of two bfloat16
 //                  numbers are exact in 32-bit, so these are the 32-bit scores of the stored queries and keys;
@@ -19,8 +20,24 @@
 namespace {
 
 constexpr int QT = 64, KT = 64;
-enum MaskKind : int { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_BLOCKS = 2 };
+enum MaskKind : int { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_BLOCKS = 2, MASK_WINDOW_POOLED = 3 };
 typedef __nv_bfloat16 bf16;
+
+// What only some mixers use: a learned sink score per query head (null: none), a cap on the scores (0: none), and the
+// averaged blocks of MASK_WINDOW_POOLED: their pages (laid out like the tokens' with one value head a key head), the
+// requests' tables of those pages and the tokens a block holds.  A row at position p sees the blocks
+// 0 .. first_key(p) / pool - 1, then the tokens first_key(p) .. p.
+struct Extras {
+    const float* sinks;
+    float softcap;
+    const bf16* pool_cache;
+    const int* pool_table;
+    int pool_bt_stride, pool;
+};
+
+__device__ __forceinline__ float capped(float s, float softcap) {
+    return softcap > 0.0f ? softcap * tanhf(s / softcap) : s;
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
@@ -53,7 +70,7 @@ __device__ __forceinline__ void split_bf16(float a, float b, uint32_t& hi, uint3
 }
 
 __device__ __forceinline__ int first_key_of(int pos, int mask_kind, int mask_size) {
-    if (mask_kind == MASK_WINDOW) return pos - mask_size + 1 > 0 ? pos - mask_size + 1 : 0;
+    if (mask_kind == MASK_WINDOW || mask_kind == MASK_WINDOW_POOLED) return pos - mask_size + 1 > 0 ? pos - mask_size + 1 : 0;
     if (mask_kind == MASK_BLOCKS) return (pos / mask_size) * mask_size;
     return 0;
 }
@@ -64,7 +81,7 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
                         const bf16* __restrict__ cache, const int* __restrict__ positions,
                         const int* __restrict__ row_start, const int* __restrict__ block_table, int bt_stride,
                         int num_seqs, int heads, int kv_heads, int page_size, int mask_kind, int mask_size, float scale,
-                        int keys_per_value, int out_f32) {
+                        int keys_per_value, int out_f32, Extras x) {
     constexpr int KS = D * 2 + 16, VS = DV * 2 + 16;              // bytes of a key row and a value row in shared memory
     constexpr int STAGE = KT * (KS + VS);
     extern __shared__ __align__(128) unsigned char tile_smem[];   // two stages of keys then values
@@ -91,12 +108,16 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
     const int head = blockIdx.y, kv_head = head / (heads / kv_heads);
     const int pos_first = positions[r0], pos_last = pos_first + n - 1;        // a sequence's rows stand at consecutive positions
     const int key_lo = first_key_of(pos_first, mask_kind, mask_size);
-    const int tiles = (pos_last - key_lo) / KT + 1;
+    // the keys the block walks: the averaged blocks its last row sees, then the tokens key_lo .. pos_last
+    const int blocks_last = mask_kind == MASK_WINDOW_POOLED ? first_key_of(pos_last, mask_kind, mask_size) / x.pool : 0;
+    const int span = blocks_last + pos_last - key_lo + 1;
+    const int tiles = (span - 1) / KT + 1;
     // keys_per_value key heads in a row read one value head: the page holds kv_heads / keys_per_value of those
     const int64_t page_elems = (int64_t)kv_heads * page_size * D + (int64_t)(kv_heads / keys_per_value) * page_size * DV;
-    const bf16* kbase = cache + (int64_t)kv_head * page_size * D;
-    const bf16* vbase = cache + (int64_t)kv_heads * page_size * D + (int64_t)(kv_head / keys_per_value) * page_size * DV;
+    const int64_t k_off = (int64_t)kv_head * page_size * D;
+    const int64_t v_off = (int64_t)kv_heads * page_size * D + (int64_t)(kv_head / keys_per_value) * page_size * DV;
     const int* table = block_table + (int64_t)seq * bt_stride;
+    const int* pool_table = x.pool_table == nullptr ? nullptr : x.pool_table + (int64_t)seq * x.pool_bt_stride;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(tile_smem);
 
     // a tile's copy: two threads a key; one takes the first half of the key's and of the value's 16-byte chunks, the
@@ -104,13 +125,16 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
     const int copy_row = tid >> 1, copy_half = tid & 1;
     auto fill = [&](int tile) {
         const uint32_t stage = smem_base + (uint32_t)(tile & 1) * STAGE;
-        const int key = key_lo + tile * KT + copy_row;
-        const bool there = key <= pos_last;
-        const int k = there ? key : pos_last;
-        const int64_t base = (int64_t)table[k / page_size] * page_elems;
+        const int at = tile * KT + copy_row;
+        const bool there = at < span;
+        const int a = there ? at : span - 1;
+        const bool averaged = a < blocks_last;
+        const int k = averaged ? a : key_lo + a - blocks_last;
+        const bf16* from = averaged ? x.pool_cache : cache;
+        const int64_t base = (int64_t)(averaged ? pool_table : table)[k / page_size] * page_elems;
         const int in_page = k % page_size;
-        const bf16* kp = kbase + base + (int64_t)in_page * D;
-        const bf16* vp = vbase + base + (int64_t)in_page * DV;
+        const bf16* kp = from + k_off + base + (int64_t)in_page * D;
+        const bf16* vp = from + v_off + base + (int64_t)in_page * DV;
         const int bytes = there ? 16 : 0;                         // (a key behind the last one is zero-filled)
         constexpr int KC = D / 8, VC = DV / 8;
 #pragma unroll
@@ -142,15 +166,20 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
             qa[ks][3] = bottom_there ? *reinterpret_cast<const uint32_t*>(bottom + ks * 16 + 2 * t + 8) : 0u;
         }
     }
-    int pos[2], first_key[2];
+    int pos[2], first_key[2], blocks[2];
     bool there[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         pos[r] = pos_first + i0 + g + r * 8;
         there[r] = i0 + g + r * 8 < n;
         first_key[r] = first_key_of(pos[r], mask_kind, mask_size);
+        blocks[r] = mask_kind == MASK_WINDOW_POOLED ? first_key[r] / x.pool : 0;
     }
     float m[2] = {-1.0e30f, -1.0e30f}, l[2] = {0.0f, 0.0f};
+    if (x.sinks != nullptr) {                                     // the sink is the start of the running softmax
+        m[0] = m[1] = x.sinks[head];
+        l[0] = l[1] = t == 0 ? 1.0f : 0.0f;                       // (a row's four lanes add their sums at the end)
+    }
     float o[DV / 8][4];
 #pragma unroll
     for (int j = 0; j < DV / 8; ++j)
@@ -167,11 +196,12 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
         }
         __syncthreads();                                          // this tile's keys and values are in shared memory
         const uint32_t kstage = smem_base + (uint32_t)(tile & 1) * STAGE, vstage = kstage + KT * KS;
-        const int key0 = key_lo + tile * KT;
+        const int at0 = tile * KT;
+        const int key0 = key_lo + at0 - blocks_last;              // the token at the tile's first place, were it one
         // a warp whose rows see none of the tile's keys skips it (the rows' positions bound what they see)
         const int warp_first = first_key_of(pos_first + i0, mask_kind, mask_size);
         const int warp_last = pos_first + min(i0 + 15, n - 1);
-        const bool any = i0 < n && key0 <= warp_last && key0 + KT - 1 >= warp_first;
+        const bool any = i0 < n && (at0 < blocks_last || (key0 <= warp_last && key0 + KT - 1 >= warp_first));
         if (any) {
             float s[KT / 8][4];
 #pragma unroll
@@ -194,9 +224,10 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
             for (int j = 0; j < KT / 8; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int r = e >> 1, key = key0 + j * 8 + 2 * t + (e & 1);
-                    const bool seen = there[r] && key <= pos[r] && key >= first_key[r];
-                    s[j][e] = seen ? s[j][e] * scale : -1.0e30f;
+                    const int r = e >> 1, place = j * 8 + 2 * t + (e & 1), key = key0 + place;
+                    const bool seen = there[r] && (at0 + place < blocks_last ? at0 + place < blocks[r]
+                                                                             : key <= pos[r] && key >= first_key[r]);
+                    s[j][e] = seen ? capped(s[j][e] * scale, x.softcap) : -1.0e30f;
                     top[r] = fmaxf(top[r], s[j][e]);
                 }
             float corr[2];
@@ -273,7 +304,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
                       const bf16* __restrict__ cache, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride, int heads,
                       int kv_heads, int page_size, int mask_kind, int mask_size, float scale, int keys_per_value,
-                      int out_f32) {
+                      int out_f32, Extras x) {
     constexpr int KS = D * 2 + 16, VS = DV * 2 + 16;
     constexpr int STAGE = KT * (KS + VS);
     constexpr int PART = DV + 2;                                  // a row's accumulator, maximum and sum
@@ -284,23 +315,30 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
     const int row = blockIdx.x, kv_head = blockIdx.y, per = heads / kv_heads;
     const int pos = positions[row], seq = seq_of_row[row];
     const int key_lo = first_key_of(pos, mask_kind, mask_size);
-    const int tiles = (pos - key_lo) / KT + 1;
+    // the keys the row sees, in the order they are walked: its averaged blocks, then the tokens key_lo .. pos
+    const int blocks = mask_kind == MASK_WINDOW_POOLED ? key_lo / x.pool : 0;
+    const int span = blocks + pos - key_lo + 1;
+    const int tiles = (span - 1) / KT + 1;
     // keys_per_value key heads in a row read one value head: the page holds kv_heads / keys_per_value of those
     const int64_t page_elems = (int64_t)kv_heads * page_size * D + (int64_t)(kv_heads / keys_per_value) * page_size * DV;
-    const bf16* kbase = cache + (int64_t)kv_head * page_size * D;
-    const bf16* vbase = cache + (int64_t)kv_heads * page_size * D + (int64_t)(kv_head / keys_per_value) * page_size * DV;
+    const int64_t k_off = (int64_t)kv_head * page_size * D;
+    const int64_t v_off = (int64_t)kv_heads * page_size * D + (int64_t)(kv_head / keys_per_value) * page_size * DV;
     const int* table = block_table + (int64_t)seq * bt_stride;
+    const int* pool_table = x.pool_table == nullptr ? nullptr : x.pool_table + (int64_t)seq * x.pool_bt_stride;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(tile_smem);
     const int copy_row = tid >> 1, copy_half = tid & 1;
     auto fill = [&](int tile) {
         const uint32_t stage = smem_base + (uint32_t)(tile & 1) * STAGE;
-        const int key = key_lo + tile * KT + copy_row;
-        const bool there = key <= pos;
-        const int k = there ? key : pos;
-        const int64_t base = (int64_t)table[k / page_size] * page_elems;
+        const int at = tile * KT + copy_row;
+        const bool there = at < span;
+        const int a = there ? at : span - 1;
+        const bool averaged = a < blocks;
+        const int k = averaged ? a : key_lo + a - blocks;
+        const bf16* from = averaged ? x.pool_cache : cache;
+        const int64_t base = (int64_t)(averaged ? pool_table : table)[k / page_size] * page_elems;
         const int in_page = k % page_size;
-        const bf16* kp = kbase + base + (int64_t)in_page * D;
-        const bf16* vp = vbase + base + (int64_t)in_page * DV;
+        const bf16* kp = from + k_off + base + (int64_t)in_page * D;
+        const bf16* vp = from + v_off + base + (int64_t)in_page * DV;
         const int bytes = there ? 16 : 0;
         constexpr int KC = D / 8, VC = DV / 8;
 #pragma unroll
@@ -330,6 +368,14 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
         }
     }
     float m[2] = {-1.0e30f, -1.0e30f}, l[2] = {0.0f, 0.0f};
+    if (x.sinks != nullptr && warp == 0) {                        // the sink is the start of ONE of the four running softmaxes
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+            if (g + r * 8 < per) {
+                m[r] = x.sinks[kv_head * per + g + r * 8];
+                l[r] = t == 0 ? 1.0f : 0.0f;
+            }
+    }
     float o[DV / 8][4];
 #pragma unroll
     for (int j = 0; j < DV / 8; ++j)
@@ -345,8 +391,8 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
         }
         __syncthreads();
         const uint32_t kstage = smem_base + (uint32_t)(tile & 1) * STAGE, vstage = kstage + KT * KS;
-        const int key0 = key_lo + tile * KT + warp * 16;         // the warp's 16 keys of the tile
-        if (key0 <= pos) {
+        const int at0 = tile * KT + warp * 16;                    // the warp's 16 keys of the tile
+        if (at0 < span) {
             float s[2][4];
 #pragma unroll
             for (int j = 0; j < 2; ++j)
@@ -364,8 +410,8 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + j * 8 + 2 * t + (e & 1);
-                    s[j][e] = key <= pos ? s[j][e] * scale : -1.0e30f;      // (every key from key_lo on is inside the mask)
+                    const int at = at0 + j * 8 + 2 * t + (e & 1);
+                    s[j][e] = at < span ? capped(s[j][e] * scale, x.softcap) : -1.0e30f;     // (all of the span is inside the mask)
                     top[e >> 1] = fmaxf(top[e >> 1], s[j][e]);
                 }
             float corr[2];
@@ -448,7 +494,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
 template <int D, int DV>
 int launch_rows(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache, const int* positions,
                 const int* seq_of_row, const int* block_table, int bt_stride, int rows, int heads, int kv_heads,
-                int page_size, int mask_kind, int mask_size, float scale, int keys_per_value, int out_f32,
+                int page_size, int mask_kind, int mask_size, float scale, int keys_per_value, int out_f32, Extras x,
                 cudaStream_t stream) {
     constexpr int smem = 2 * KT * (D * 2 + 16 + DV * 2 + 16) + 4 * 16 * (DV + 2) * 4;
     auto kernel = attention_rows_kernel<D, DV>;
@@ -459,14 +505,15 @@ int launch_rows(const void* q, int64_t q_stride, void* out, int64_t out_stride, 
     cudaError_t launched = tb_launch_pdl(kernel, dim3(rows, kv_heads), dim3(128), (size_t)smem, stream, (const bf16*)q,
                                          q_stride, (bf16*)out, out_stride, (const bf16*)cache, positions, seq_of_row,
                                          block_table, bt_stride, heads, kv_heads, page_size, mask_kind, mask_size, scale,
-                                         keys_per_value, out_f32);
+                                         keys_per_value, out_f32, x);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
 template <int D, int DV>
 int launch(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache, const int* positions,
            const int* row_start, const int* block_table, int bt_stride, int rows, int num_seqs, int heads, int kv_heads,
-           int page_size, int mask_kind, int mask_size, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
+           int page_size, int mask_kind, int mask_size, float scale, int keys_per_value, int out_f32, Extras x,
+           cudaStream_t stream) {
     constexpr int smem = 2 * KT * (D * 2 + 16 + DV * 2 + 16);
     auto kernel = attention_prompt_kernel<D, DV>;
     if (smem > 40 * 1024) {
@@ -477,7 +524,7 @@ int launch(const void* q, int64_t q_stride, void* out, int64_t out_stride, const
     cudaError_t launched = tb_launch_pdl(kernel, grid, dim3(128), (size_t)smem, stream, (const bf16*)q, q_stride,
                                          (bf16*)out, out_stride, (const bf16*)cache, positions, row_start, block_table,
                                          bt_stride, num_seqs, heads, kv_heads, page_size, mask_kind, mask_size, scale,
-                                         keys_per_value, out_f32);
+                                         keys_per_value, out_f32, x);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
@@ -492,24 +539,34 @@ TB_EXPORT int tb_attention_prompt_mma_supported(int dim, int vdim) {
 // unrounded), [rows, heads * vdim], row stride out_stride in its own elements; cache: this layer's pages
 // ([kv_heads][page_size][dim] keys then [kv_heads / keys_per_value][page_size][vdim] values a page, key head g reading
 // value head g / keys_per_value); row_start: int32 [num_seqs + 1]; the rows of a sequence stand at consecutive
-// positions.  mask_kind: 0 causal, 1 window, 2 blocks.
+// positions.  mask_kind: 0 causal, 1 window, 2 blocks, 3 window with averaged blocks (pool_cache: the layer's pages of
+// averages, pool_table: the requests' tables of those pages with row stride pool_bt_stride, pool: tokens a block).
+// sinks: null or float32 [heads]; softcap: 0 for none.
 TB_EXPORT int tb_attention_prompt_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
                                       const int* positions, const int* row_start, const int* block_table, int bt_stride,
                                       int rows, int num_seqs, int heads, int kv_heads, int dim, int vdim, int page_size,
                                       int mask_kind, int mask_size, float scale, int keys_per_value, int out_f32,
-                                      cudaStream_t stream) {
+                                      const float* sinks, float softcap, const void* pool_cache, const int* pool_table,
+                                      int pool_bt_stride, int pool, cudaStream_t stream) {
     if (rows == 0) return 0;
+    if (mask_kind == MASK_WINDOW_POOLED && (pool < 1 || pool_cache == nullptr || pool_table == nullptr || keys_per_value != 1 ||
+                                            (uintptr_t)pool_cache % 16 != 0))
+        return TB_ERR_BAD_SIZE;
+    if (softcap < 0.0f) return TB_ERR_BAD_SIZE;
+    Extras x;
+    x.sinks = sinks; x.softcap = softcap; x.pool_cache = (const bf16*)pool_cache; x.pool_table = pool_table;
+    x.pool_bt_stride = pool_bt_stride; x.pool = pool;
     if (!tb_attention_prompt_mma_supported(dim, vdim)) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || page_size < 1 || num_seqs < 1) return TB_ERR_BAD_SIZE;
     if (keys_per_value < 1 || kv_heads % keys_per_value != 0) return TB_ERR_BAD_SIZE;
     if (heads > 65535) return TB_ERR_BAD_SIZE;
-    if (mask_kind < MASK_CAUSAL || mask_kind > MASK_BLOCKS) return TB_ERR_BAD_SIZE;
+    if (mask_kind < MASK_CAUSAL || mask_kind > MASK_WINDOW_POOLED) return TB_ERR_BAD_SIZE;
     if (mask_kind != MASK_CAUSAL && mask_size < 1) return TB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 2 != 0 || out_stride % 2 != 0)
         return TB_ERR_BAD_ALIGN;
 #define TB_ATTEND(D, DV)                                                                                            \
     return launch<D, DV>(q, q_stride, out, out_stride, cache, positions, row_start, block_table, bt_stride, rows,    \
-                         num_seqs, heads, kv_heads, page_size, mask_kind, mask_size, scale, keys_per_value, out_f32, stream)
+                         num_seqs, heads, kv_heads, page_size, mask_kind, mask_size, scale, keys_per_value, out_f32, x, stream)
     if (dim == 64 && vdim == 48) TB_ATTEND(64, 48);
     if (dim == 64 && vdim == 64) TB_ATTEND(64, 64);
     if (dim == 64 && vdim == 128) TB_ATTEND(64, 128);
@@ -523,18 +580,27 @@ TB_EXPORT int tb_attention_prompt_mma(const void* q, int64_t q_stride, void* out
 TB_EXPORT int tb_attention_rows_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
                                     const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
                                     int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
-                                    int mask_size, float scale, int keys_per_value, int out_f32, cudaStream_t stream) {
+                                    int mask_size, float scale, int keys_per_value, int out_f32, const float* sinks,
+                                    float softcap, const void* pool_cache, const int* pool_table, int pool_bt_stride,
+                                    int pool, cudaStream_t stream) {
     if (rows == 0) return 0;
+    if (mask_kind == MASK_WINDOW_POOLED && (pool < 1 || pool_cache == nullptr || pool_table == nullptr || keys_per_value != 1 ||
+                                            (uintptr_t)pool_cache % 16 != 0))
+        return TB_ERR_BAD_SIZE;
+    if (softcap < 0.0f) return TB_ERR_BAD_SIZE;
+    Extras x;
+    x.sinks = sinks; x.softcap = softcap; x.pool_cache = (const bf16*)pool_cache; x.pool_table = pool_table;
+    x.pool_bt_stride = pool_bt_stride; x.pool = pool;
     if (!tb_attention_prompt_mma_supported(dim, vdim)) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || heads / kv_heads > 16 || page_size < 1) return TB_ERR_BAD_SIZE;
     if (keys_per_value < 1 || kv_heads % keys_per_value != 0) return TB_ERR_BAD_SIZE;
     if (kv_heads > 65535) return TB_ERR_BAD_SIZE;
-    if (mask_kind < MASK_CAUSAL || mask_kind > MASK_BLOCKS) return TB_ERR_BAD_SIZE;
+    if (mask_kind < MASK_CAUSAL || mask_kind > MASK_WINDOW_POOLED) return TB_ERR_BAD_SIZE;
     if (mask_kind != MASK_CAUSAL && mask_size < 1) return TB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 2 != 0) return TB_ERR_BAD_ALIGN;
 #define TB_ROWS(D, DV)                                                                                              \
     return launch_rows<D, DV>(q, q_stride, out, out_stride, cache, positions, seq_of_row, block_table, bt_stride,   \
-                              rows, heads, kv_heads, page_size, mask_kind, mask_size, scale, keys_per_value, out_f32, stream)
+                              rows, heads, kv_heads, page_size, mask_kind, mask_size, scale, keys_per_value, out_f32, x, stream)
     if (dim == 64 && vdim == 48) TB_ROWS(64, 48);
     if (dim == 64 && vdim == 64) TB_ROWS(64, 64);
     if (dim == 64 && vdim == 128) TB_ROWS(64, 128);

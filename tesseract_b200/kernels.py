@@ -834,17 +834,7 @@ def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_masked cache")
     if gate is not None:
         _need(gate.stride(1) == 1 and gate.shape == (rows, heads * vdim) and gate.dtype == q.dtype, "attention_masked gate")
-    if sinks is not None:
-        _cuda(sinks)
-        _need(sinks.dtype == torch.float32 and sinks.numel() == heads and sinks.is_contiguous(), "attention_masked sinks")
-    pool_cache = pool_table = None
-    pool = 0
-    if mask_kind == MASK_WINDOW_POOLED:
-        _need(pooled is not None and keys_per_value == 1, "attention_masked: a pooled window needs the pooled pages")
-        pool_cache, pool_table, pool = pooled
-        _cuda(pool_cache, pool_table)
-        _need(pool_cache.dtype == q.dtype and pool_cache.is_contiguous() and pool_table.dtype == torch.int32
-              and pool_table.stride(1) == 1 and pool >= 1, "attention_masked pooled pages")
+    extras = _mask_extras("attention_masked", q, heads, mask_kind, keys_per_value, sinks, pooled)
     lib = load_library("attention_masked")
     _check(lib.tb_attention_masked(_ptr(q), _i64(q.stride(0)), _ptr(gate), _i64(gate.stride(0) if gate is not None else 0),
                                    _ptr(out), _i64(out.stride(0)), _ptr(cache), _ptr(positions), _ptr(seq_of_row),
@@ -852,10 +842,24 @@ def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
                                    _i32(kv_heads), _i32(dim), _i32(vdim), _i32(page_size), _i32(mask_kind),
                                    _i32(mask_size), _i32(1 if sink else 0), _f32(scale), _i32(keys_per_value),
                                    _i32(1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0),
-                                   _ptr(sinks), _f32(softcap), _ptr(pool_cache), _ptr(pool_table),
-                                   _i32(pool_table.stride(0) if pool_table is not None else 0), _i32(pool),
-                                   _i32(_code(q.dtype)), _stream()), "attention_masked")
+                                   _ptr(sinks), _f32(softcap), *extras, _i32(_code(q.dtype)), _stream()), "attention_masked")
     return out
+
+
+def _mask_extras(what: str, q: torch.Tensor, heads: int, mask_kind: int, keys_per_value: int, sinks, pooled):
+    """The arguments a learned sink and pooled blocks add to an attention kernel's call, checked."""
+    if sinks is not None:
+        _cuda(sinks)
+        _need(sinks.dtype == torch.float32 and sinks.numel() == heads and sinks.is_contiguous(), f"{what} sinks")
+    pool_cache = pool_table = None
+    pool = 0
+    if mask_kind == MASK_WINDOW_POOLED:
+        _need(pooled is not None and keys_per_value == 1, f"{what}: a pooled window needs the pooled pages")
+        pool_cache, pool_table, pool = pooled
+        _cuda(pool_cache, pool_table)
+        _need(pool_cache.dtype == q.dtype and pool_cache.is_contiguous() and pool_table.dtype == torch.int32
+              and pool_table.stride(1) == 1 and pool >= 1, f"{what} pooled pages")
+    return (_ptr(pool_cache), _ptr(pool_table), _i32(pool_table.stride(0) if pool_table is not None else 0), _i32(pool))
 
 
 def attention_prompt_mma_supported(dtype: torch.dtype, dim: int, vdim: int) -> bool:
@@ -867,8 +871,9 @@ def attention_prompt_mma_supported(dtype: torch.dtype, dim: int, vdim: int) -> b
 def attention_prompt_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
                          row_start: torch.Tensor, block_table: torch.Tensor, *, num_seqs: int, heads: int,
                          kv_heads: int, dim: int, vdim: int, page_size: int, mask_kind: int, mask_size: int,
-                         scale: float, keys_per_value: int = 1) -> torch.Tensor:
-    """:func:`attention_masked` (no sink, no gate) for bfloat16 prompt portions on the tensor cores: scores from
+                         scale: float, keys_per_value: int = 1, sinks: Optional[torch.Tensor] = None,
+                         softcap: float = 0.0, pooled=None) -> torch.Tensor:
+    """:func:`attention_masked` (no fixed sink, no gate; ``sinks``, ``softcap`` and ``pooled`` as there) for bfloat16 prompt portions on the tensor cores: scores from
     exact bfloat16 products with 32-bit accumulation, 32-bit softmax, the 32-bit weights split in two bfloat16 halves
     for the product with the values.  The rows of a sequence (``row_start``) stand at consecutive positions.  ``out`` in
     bfloat16 or float32 (the weighted sums unrounded); ``keys_per_value`` key heads in a row share a value head."""
@@ -880,12 +885,14 @@ def attention_prompt_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
     _need(keys_per_value >= 1 and kv_heads % keys_per_value == 0, "attention_prompt_mma keys_per_value")
     _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_prompt_mma cache")
     _need(row_start.dtype == torch.int32 and row_start.numel() >= num_seqs + 1, "attention_prompt_mma row_start")
+    extras = _mask_extras("attention_prompt_mma", q, heads, mask_kind, keys_per_value, sinks, pooled)
     lib = load_library("attention_prompt_mma")
     _check(lib.tb_attention_prompt_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                        _ptr(positions), _ptr(row_start), _ptr(block_table), _i32(block_table.stride(0)),
                                        _i32(rows), _i32(num_seqs), _i32(heads), _i32(kv_heads), _i32(dim), _i32(vdim),
                                        _i32(page_size), _i32(mask_kind), _i32(mask_size), _f32(scale),
-                                       _i32(keys_per_value), _i32(1 if out.dtype == torch.float32 else 0), _stream()),
+                                       _i32(keys_per_value), _i32(1 if out.dtype == torch.float32 else 0), _ptr(sinks),
+                                       _f32(softcap), *extras, _stream()),
            "attention_prompt_mma")
     return out
 
@@ -893,7 +900,8 @@ def attention_prompt_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
 def attention_rows_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
                        seq_of_row: torch.Tensor, block_table: torch.Tensor, *, heads: int, kv_heads: int, dim: int,
                        vdim: int, page_size: int, mask_kind: int, mask_size: int, scale: float,
-                       keys_per_value: int = 1) -> torch.Tensor:
+                       keys_per_value: int = 1, sinks: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                       pooled=None) -> torch.Tensor:
     """:func:`attention_prompt_mma` for steps of few rows at any positions: a block a (row, kv head), the kv head's
     query heads (at most 16) side by side in the tensor-core tile."""
     _cuda(q, out, cache, positions, seq_of_row, block_table)
@@ -903,12 +911,14 @@ def attention_rows_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
           "attention_rows_mma out")
     _need(keys_per_value >= 1 and kv_heads % keys_per_value == 0, "attention_rows_mma keys_per_value")
     _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_rows_mma cache")
+    extras = _mask_extras("attention_rows_mma", q, heads, mask_kind, keys_per_value, sinks, pooled)
     lib = load_library("attention_prompt_mma")
     _check(lib.tb_attention_rows_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                      _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
                                      _i32(rows), _i32(heads), _i32(kv_heads), _i32(dim), _i32(vdim), _i32(page_size),
                                      _i32(mask_kind), _i32(mask_size), _f32(scale), _i32(keys_per_value),
-                                     _i32(1 if out.dtype == torch.float32 else 0), _stream()), "attention_rows_mma")
+                                     _i32(1 if out.dtype == torch.float32 else 0), _ptr(sinks), _f32(softcap), *extras,
+                                     _stream()), "attention_rows_mma")
     return out
 
 

@@ -145,6 +145,10 @@ def ladedra_kernel_libraries(cfg: LadedraConfig, dtype: str):
 
         from .. import kernels
 
+        if any(isinstance(layer.mixer, LadedraParallel)
+               and kernels.attention_prompt_mma_supported(torch.bfloat16, layer.mixer.left.dim, layer.mixer.left.vdim)
+               for layer in cfg.layers):
+            shared.append("attention_prompt_mma")     # (head sizes the tensor-core attention takes)
         if any(isinstance(layer.mixer, LadedraLatentAttention)
                and kernels.attention_latent_mma_supported(torch.bfloat16, layer.mixer.kv_rank + layer.mixer.rot_dim,
                                                           layer.mixer.kv_rank) for layer in cfg.layers):

@@ -138,10 +138,7 @@ class NormedAttention(Mixer):
                                  window=self.mask_size if self.mask_kind == "window" else None)
 
     def attention_choice(self, rows: int) -> str:
-        """The attention kernel of a step of ``rows`` rows: the tensor-core kernels know neither a cap, a learned sink
-        nor pooled blocks."""
-        if self.softcap or self.sinks is not None or self.mask_kind == "window_pooled":
-            return "attention_masked"
+        """The attention kernel of a step of ``rows`` rows (all three know the cap, the learned sink and pooled blocks)."""
         return plan.masked_attention(self.runtime.dtype, rows, self.key_dim, self.value_dim,
                                      heads_per_kv=self.num_heads // self.num_kv_heads)
 
@@ -165,7 +162,7 @@ class NormedAttention(Mixer):
                                 amplitude=self.amplitude, heads=self.num_heads, kv_heads=self.num_kv_heads,
                                 dim=self.key_dim, vdim=self.value_dim, rot_dims=self.rot_dims,
                                 unit_norm=self.unit_norm, eps=self.qk_norm_eps, page_size=cache.page_size)
-        extras = {}
+        extras = {"sinks": self.sinks, "softcap": self.softcap}
         if pooled is not None:
             pool_table = ctx.groups[pooled.group].block_table
             kernels.pool_blocks(cache.storage, pooled.storage, ctx.positions, ctx.seq_of_row, group.block_table, pool_table,
@@ -178,16 +175,16 @@ class NormedAttention(Mixer):
             kernels.attention_rows_mma(q, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
                                        heads=self.num_heads, kv_heads=self.num_kv_heads, dim=self.key_dim,
                                        vdim=self.value_dim, page_size=cache.page_size, mask_kind=_MASKS[self.mask_kind],
-                                       mask_size=self.mask_size, scale=self.scale)
+                                       mask_size=self.mask_size, scale=self.scale, **extras)
         elif choice == "attention_prompt_mma":
             kernels.attention_prompt_mma(q, attended, cache.storage, ctx.positions, ctx.row_start, group.block_table,
                                          num_seqs=ctx.num_seqs, heads=self.num_heads, kv_heads=self.num_kv_heads,
                                          dim=self.key_dim, vdim=self.value_dim, page_size=cache.page_size,
-                                         mask_kind=_MASKS[self.mask_kind], mask_size=self.mask_size, scale=self.scale)
+                                         mask_kind=_MASKS[self.mask_kind], mask_size=self.mask_size, scale=self.scale,
+                                         **extras)
         else:
             kernels.attention_masked(q, None, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
                                      heads=self.num_heads, kv_heads=self.num_kv_heads, dim=self.key_dim,
                                      vdim=self.value_dim, page_size=cache.page_size, mask_kind=_MASKS[self.mask_kind],
-                                     mask_size=self.mask_size, sink=False, scale=self.scale, sinks=self.sinks,
-                                     softcap=self.softcap, **extras)
+                                     mask_size=self.mask_size, sink=False, scale=self.scale, **extras)
         return self.o_proj.forward(attended, float32_out=self.stream_f32)

@@ -738,7 +738,9 @@ def test_random_configurations_match_plain_in_float32(tmp_path, seed):
     for name, steps in (("whole", trace_whole(requests)), ("tail", trace_tail(requests, tail=20)),
                         ("portions", trace_portions(requests)), ("mixed", trace_mixed(requests, seed=seed, live_max=4))):
         stepper = make_stepper(model, capacity_tokens=max(1024, max_live_tokens(steps)), max_requests=4)
-        replay_against_plain(stepper, steps, folder, requests, "float32", f"seed {seed}/{name}")
+        # (drawn models hold ill-conditioned spots, a head whose output the norm per head divides by almost nothing, say:
+        # 32-bit rounding shows there at up to 1e-4 of the largest logit; a lost key or a reach one off moves percents)
+        compare(replay(stepper, steps), plain_rows(folder, requests, "float32")[0], 1e-4, f"seed {seed}/{name}")
         assert stepper.cache.used_pages() == 0
 
 
