@@ -664,7 +664,7 @@ def run_kernels(args):
 
 
 # ----------------------------------------------------------------------------- another design beside Llama
-# `--design revesun|pekodra|kazodra`: prefill and decode of a model of that design at layer sizes like a real model's (random
+# `--design revesun|pekodra|kazodra|ladedra`: prefill and decode of a model of that design at layer sizes like a real model's (random
 # weights), beside a Llama (and, for Pekodra, a Revesun: the other design with a 32-bit stream) of the same width, heads, head sizes, layer count and about as many weights a layer, measured the
 # same way; then the design's own kernels alone, against the bytes they must move.  The default workload is untouched.
 DESIGN_SIZES = {
@@ -762,6 +762,46 @@ def kazodra_config(size, layers):
     return config
 
 
+LADEDRA_SIZES = {
+    # (layers alternate between latent attention with a dense feed-forward and the two mixers side by side with routed
+    # experts; the window attention has the heads of the models beside it; a gated expert has three matrices where
+    # Pekodra's has two, so its inner size is about two thirds of that one's)
+    "1b": dict(window=512, pool=64, rank=512, rot=64, latent_heads=16, latent_dim=128, ret_heads=16, ret_dim=128,
+               dense_ff=8192, experts=32, top=4, groups=(4, 2), expert_ff=640, shared_ff=1408),
+    "3b": dict(window=512, pool=64, rank=512, rot=64, latent_heads=24, latent_dim=128, ret_heads=24, ret_dim=128,
+               dense_ff=8192, experts=32, top=4, groups=(4, 2), expert_ff=640, shared_ff=1408),
+    "8b": dict(window=512, pool=64, rank=512, rot=64, latent_heads=32, latent_dim=128, ret_heads=32, ret_dim=128,
+               dense_ff=14336, experts=32, top=4, groups=(4, 2), expert_ff=1408, shared_ff=2752),
+}
+
+
+def ladedra_config(size, layers):
+    """Even layers: causal latent attention (stretched pair rotation, output gate) and a dense squared-ReLU feed-forward;
+    odd layers: window attention with averaged blocks, a sink and capped scores beside retention, and routed gated experts
+    in groups with a shared expert."""
+    z, p = DESIGN_SIZES[size], LADEDRA_SIZES[size]
+    heads = p["ret_heads"]
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": p["latent_heads"], "dim": p["latent_dim"], "rot_dim": p["rot"], "vdim": p["latent_dim"],
+                        "kv_rank": p["rank"], "scale": (p["latent_dim"] + p["rot"]) ** -0.5,
+                        "rot": {"dims": p["rot"], "base": 10000.0,
+                                "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}},
+              "mlp": {"kind": "dense", "ff": p["dense_ff"]}}
+    parallel = {"type": "parallel",
+                "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                   "mask": {"size": p["window"], "pool": p["pool"]}, "scale": z["dim"] ** -0.5 * 4.0,
+                                   "softcap": 30.0, "rot": {"dims": z["dim"], "base": 500000.0}},
+                          "right": {"heads": heads, "dim": p["ret_dim"], "vdim": p["ret_dim"],
+                                    "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, heads - 1)) for h in range(heads)],
+                                    "rot": {"dims": p["ret_dim"], "base": 10000.0}},
+                          "left_scale": 1.0, "right_scale": 1.0},
+                "mlp": {"kind": "moe", "router": {"experts": p["experts"], "top": p["top"], "scale": 2.5,
+                                                  "groups": {"count": p["groups"][0], "keep": p["groups"][1]}},
+                        "expert": {"ff": p["expert_ff"]}, "shared": {"ff": p["shared_ff"]}}}
+    return {"architecture": "Ladedra", "torch_dtype": "bfloat16", "width": z["width"], "vocab": DESIGN_VOCAB,
+            "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "layers": [parallel if i % 2 else latent for i in range(layers)]}
+
+
 def run_design(args):
     import numpy as np
     import torch
@@ -844,7 +884,8 @@ def run_design(args):
         scratch.cleanup()
         return out
 
-    result = {"design": {"revesun": "Revesun", "pekodra": "Pekodra", "kazodra": "Kazodra"}[args.design], "size": args.size,
+    result = {"design": {"revesun": "Revesun", "pekodra": "Pekodra", "kazodra": "Kazodra", "ladedra": "Ladedra"}[args.design],
+              "size": args.size,
               "layers": layers,
               "vocab": DESIGN_VOCAB, "dtype": "bf16", "data": "synthetic",
               "l2": "a 256 MB buffer is written between timed prefill steps; a decode step reads its weights, which "
@@ -856,6 +897,17 @@ def run_design(args):
             result["llama"] = measure(llama)
         if args.only in ("all", "kernels"):
             result["kernels"] = kazodra_kernels(args.size, pk)
+        result["clocks"] = sampler.stop(windows)
+        result["peaks"] = pk
+        print(json.dumps(result))
+        return 0
+    if args.design == "ladedra":                   # beside Pekodra: window attention, routed experts, a 32-bit stream
+        if args.only in ("all", "decode", "prefill"):
+            result["ladedra"] = measure(ladedra_config(args.size, layers))
+            result["pekodra"] = measure(pekodra_config(args.size, layers))
+            result["llama"] = measure(llama)
+        if args.only in ("all", "kernels"):
+            result["kernels"] = ladedra_kernels(args.size, pk)
         result["clocks"] = sampler.stop(windows)
         result["peaks"] = pk
         print(json.dumps(result))
@@ -1176,6 +1228,236 @@ def kazodra_kernels(size, pk):
     return out
 
 
+def time_launches(pk, out, name, make, nbytes, flops=0, tensor=False, sets=8):
+    """Device time of one launch of ``make(k)()``: a CUDA graph of ``sets`` launches over as many buffer sets (together
+    larger than L2), median of seven replays; the bytes the launch must move against the measured copy bandwidth, and
+    its useful multiply-adds against the measured bfloat16 product rate where it runs on the tensor cores."""
+    import torch
+
+    runs = [make(k) for k in range(sets)]
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for run in runs:
+            run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()                 # one graph of the launches: no host time between them
+    with torch.cuda.graph(graph):
+        for run in runs:
+            run()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(7):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop) * 1e3 / sets)
+    us = statistics.median(times)
+    line = {"us": round(us, 2), "mb": round(nbytes / 1e6, 2), "gbs": round(nbytes / us / 1e3, 1),
+            "frac_of_measured_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+    if flops:
+        line["tflops"] = round(flops / us / 1e6, 2)
+        if tensor:
+            line["frac_of_measured_bf16"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
+    out[name] = line
+
+
+def ladedra_kernels(size, pk):
+    """Ladedra's own kernels alone at this size, timed like :func:`design_kernels`: 2,048 prompt rows of one sequence,
+    and 64 and 8 decoded rows at context 2,048."""
+    import torch
+
+    from tesseract_b200 import kernels
+    from tesseract_b200.parts import Runtime
+    from tesseract_b200.parts.linear import Linear
+    from tesseract_b200.parts.rotary import blended_inverse_frequencies
+
+    z, p = DESIGN_SIZES[size], LADEDRA_SIZES[size]
+    dev = "cuda"
+    W, page = z["width"], PAGE_SIZE
+    H, G, d = z["heads"], z["kv_heads"], z["dim"]
+    LH, ld, rank, rot, window, pool = p["latent_heads"], p["latent_dim"], p["rank"], p["rot"], p["window"], p["pool"]
+    RH, rd = p["ret_heads"], p["ret_dim"]
+    E, top, EF, groups, keep = p["experts"], p["top"], p["expert_ff"], p["groups"][0], p["groups"][1]
+    entry = rank + rot
+    half_freq = torch.tensor([5e5 ** (-2.0 * i / d) for i in range(d // 2)], dtype=torch.float32, device=dev)
+    ret_freq = torch.tensor([1e4 ** (-2.0 * i / rd) for i in range(rd // 2)], dtype=torch.float32, device=dev)
+    freqs, amplitude = blended_inverse_frequencies(rot, 1e4, {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0})
+    pair_freq = torch.tensor(freqs, dtype=torch.float32, device=dev)
+    out = {}
+
+    def timed(name, make, nbytes, flops=0, tensor=False):
+        time_launches(pk, out, name, make, nbytes, flops, tensor)
+
+    for label, rows, seqs, begin in (("prefill_2048", 2048, 1, 0), ("decode_64", 64, 64, 2047), ("decode_8", 8, 8, 2047)):
+        new = rows // seqs
+        positions = (torch.arange(rows, dtype=torch.int32, device=dev) % new) + begin
+        seq_of_row = torch.arange(rows, dtype=torch.int32, device=dev) // new
+        row_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * new
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        pages_per_seq = 2048 // page
+        table = (torch.arange(seqs * pages_per_seq, dtype=torch.int32, device=dev) + 1).view(seqs, pages_per_seq)
+        pool_pages = -(-(2048 // pool) // page)
+        pool_table = (torch.arange(seqs * pool_pages, dtype=torch.int32, device=dev) + 1).view(seqs, pool_pages)
+        page_elems = G * page * 2 * d
+
+        def join(k):
+            res, upd, gate = (torch.randn(rows, W, device=dev) for _ in range(3))
+            bias, scale, w = torch.zeros(W, device=dev), torch.ones(W, device=dev), torch.ones(W, device=dev)
+            y = torch.empty(rows, W, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.gated_add_norm(res, upd, gate, bias, scale, w, y, 1e-5)
+
+        timed(f"gated_add_norm (scale, gate, add, norm)/{label}", join, rows * W * (4 * 4 + 2))
+
+        def rotate(k):
+            proj = torch.randn(rows, (H + 2 * G) * d, device=dev).bfloat16()
+            q = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+            cache = torch.zeros(seqs * pages_per_seq + 1, page_elems, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.rope_norm_cache(proj, q, cache, positions, seq_of_row, table, half_freq, amplitude=1.0,
+                                                   heads=H, kv_heads=G, dim=d, vdim=d, rot_dims=d, unit_norm=True, eps=1e-5,
+                                                   page_size=page)
+
+        timed(f"rope_norm_cache/{label}", rotate, rows * (H + 2 * G) * d * 2 * 2)
+
+        def average(k):
+            cache = torch.randn(seqs * pages_per_seq + 1, page_elems, device=dev).bfloat16()
+            pooled = torch.zeros(seqs * pool_pages + 1, page_elems, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.pool_blocks(cache, pooled, positions, seq_of_row, table, pool_table, kv_heads=G, dim=d,
+                                               vdim=d, page_size=page, pool=pool)
+
+        ending = sum(1 for q in positions.tolist() if (q + 1) % pool == 0)
+        timed(f"pool_blocks/{label}", average, ending * G * 2 * d * 2 * (pool + 1) + rows * 4)
+
+        seen = sum(min(int(q), window - 1) + 1 + max(0, int(q) - window + 1) // pool for q in positions.tolist())
+        read = (2048 if new > 1 else seqs * (min(begin + 1, window) + max(0, begin - window + 1) // pool)) * G * 2 * d * 2
+        sinks = torch.randn(H, device=dev)
+
+        def attend(kernel):
+            def make(k):
+                q = torch.randn(rows, H * d, device=dev).bfloat16()
+                o = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+                cache = torch.randn(seqs * pages_per_seq + 1, page_elems, device=dev).bfloat16()
+                pooled = torch.randn(seqs * pool_pages + 1, page_elems, device=dev).bfloat16()
+                common = dict(heads=H, kv_heads=G, dim=d, vdim=d, page_size=page, mask_kind=kernels.MASK_WINDOW_POOLED,
+                              mask_size=window, scale=d ** -0.5, sinks=sinks, softcap=30.0, pooled=(pooled, pool_table, pool))
+                if kernel == "attention_prompt_mma":
+                    return lambda: kernels.attention_prompt_mma(q, o, cache, positions, row_start, table, num_seqs=seqs, **common)
+                if kernel == "attention_rows_mma":
+                    return lambda: kernels.attention_rows_mma(q, o, cache, positions, seq_of_row, table, **common)
+                return lambda: kernels.attention_masked(q, None, o, cache, positions, seq_of_row, table, sink=False, **common)
+            return make
+
+        for kernel in ("attention_masked", "attention_prompt_mma" if new > 1 else "attention_rows_mma"):
+            if kernel != "attention_masked" and not kernels.attention_prompt_mma_supported(torch.bfloat16, d, d):
+                continue
+            timed(f"{kernel} (window {window}, blocks of {pool}, sink, cap)/{label}", attend(kernel),
+                  rows * H * d * 2 * 2 + read, flops=seen * H * 4 * d, tensor=kernel != "attention_masked")
+
+        def prepare(k):
+            proj = torch.randn(rows, RH * 4 * rd, device=dev).bfloat16()
+            y = torch.empty(rows, RH * 3 * rd, device=dev)
+            return lambda: kernels.retention_prepare(proj, y, positions, ret_freq, heads=RH, dim=rd, vdim=rd, rot_dims=rd,
+                                                     amplitude=1.0, k_scale=rd ** -0.5)
+
+        timed(f"retention_prepare/{label}", prepare, rows * RH * 3 * rd * (2 + 4))
+
+        def recurrence(k):
+            rows_in = torch.randn(rows, RH * 3 * rd, device=dev)
+            decay = torch.full((RH,), 0.99, device=dev)
+            state = torch.zeros(seqs + 1, RH, rd, rd, device=dev)
+            y = torch.empty(rows, RH * rd, device=dev)
+            return lambda: kernels.lightning(rows_in, decay, state, y, row_start, slots, num_seqs=seqs, heads=RH, dim=rd,
+                                             vdim=rd, max_new=new, activation=False)
+
+        timed(f"lightning (32-bit rows, no activation)/{label}", recurrence,
+              rows * RH * 4 * rd * 4 + seqs * RH * rd * rd * 4 * 2, flops=rows * RH * rd * rd * 4 + (rows * min(new, 64) * RH * rd * 2 if new > 1 else 0))
+
+        def head_norm(k):
+            o = torch.randn(rows, RH * rd, device=dev)
+            gate = torch.randn(rows, RH * rd, device=dev).bfloat16()
+            y = torch.empty(rows, RH * rd, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.head_norm_gate(o, gate, y, heads=RH, vdim=rd, eps=1e-5, gate_kind=kernels.GATE_SILU)
+
+        timed(f"head_norm_gate/{label}", head_norm, rows * RH * rd * (4 + 2 + 2))
+
+        def blend(k):
+            a, b = torch.randn(rows, W, device=dev), torch.randn(rows, W, device=dev)
+            return lambda: kernels.blend_rows(a, b, 1.2, 0.9)
+
+        timed(f"blend_rows/{label}", blend, rows * W * 4 * 3)
+
+        def latent_write(k):
+            down = torch.randn(rows, entry, device=dev)
+            q = torch.randn(rows, LH * (ld + rot), device=dev).bfloat16()
+            q_full = torch.empty(rows, LH * entry, dtype=torch.bfloat16, device=dev)
+            w = torch.ones(rank, device=dev)
+            cache = torch.zeros(seqs * pages_per_seq + 1, page * entry, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.latent_rope_cache(down, q, q_full, cache, w, positions, seq_of_row, table, pair_freq,
+                                                     heads=LH, dim=ld, rank=rank, rot_width=rot, rot_dims=rot,
+                                                     page_size=page, eps=1e-5, amplitude=amplitude)
+
+        timed(f"latent_rope_cache/{label}", latent_write, rows * (entry * (4 + 2) + LH * rot * 2 * 2))
+
+        causal_keys = sum(int(q) + 1 for q in positions.tolist())
+        latent_read = (2048 if new > 1 else seqs * (begin + 1)) * entry * 2
+
+        def latent_attend(k):
+            q_full = torch.randn(rows, LH * entry, device=dev).bfloat16()
+            mixed = torch.empty(rows, LH * rank, dtype=torch.bfloat16, device=dev)
+            cache = torch.randn(seqs * pages_per_seq + 1, page * entry, device=dev).bfloat16()
+            return lambda: kernels.attention_latent_mma(q_full, mixed, cache, positions, seq_of_row, table, heads=LH,
+                                                        dim=entry, vdim=rank, page_size=page, mask_kind=kernels.MASK_CAUSAL,
+                                                        mask_size=0, scale=(ld + rot) ** -0.5)
+
+        if kernels.attention_latent_mma_supported(torch.bfloat16, entry, rank):
+            timed(f"attention_latent_mma (causal)/{label}", latent_attend, rows * LH * (entry + rank) * 2 + latent_read,
+                  flops=causal_keys * LH * 2 * (entry + rank), tensor=True)
+
+        def out_gate(k):
+            a, g = (torch.randn(rows, LH * ld, device=dev).bfloat16() for _ in range(2))
+            return lambda: kernels.sigmoid_mul(a, g, a)
+
+        timed(f"sigmoid_mul/{label}", out_gate, rows * LH * ld * 2 * 3)
+
+        def route(k):
+            x = torch.randn(rows, W, device=dev).bfloat16()
+            router = Linear(torch.randn(E, W).bfloat16(), Runtime(torch.bfloat16, torch.device(dev)))
+            ids = torch.empty(rows, top, dtype=torch.int32, device=dev)
+            weights = torch.empty(rows, top, dtype=torch.float32, device=dev)
+            return lambda: kernels.choose_grouped(router.forward(x, float32_out=True), ids, weights, groups=groups, keep=keep,
+                                                  weight_scale=2.5)
+
+        timed(f"router (product with 32-bit logits, choice among groups)/{label}", route, rows * W * 2 + E * W * 2,
+              flops=rows * E * W * 2)
+
+        ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).to(torch.int32).contiguous()
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        order = torch.empty(rows * top, dtype=torch.int32, device=dev)
+        kernels.expert_plan(ids, E, offsets, order)
+        used = min(E, rows * top)                      # experts whose weights a step must read
+
+        def experts_up(k):
+            x = torch.randn(rows, W, device=dev).bfloat16()
+            up = torch.randn(E, 2 * EF, W, device=dev).bfloat16()
+            hidden = torch.empty(rows * top, 2 * EF, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.expert_linear(x, up, hidden, offsets, order, source_div=top)
+
+        timed(f"expert_linear gate and up/{label}", experts_up, used * 2 * EF * W * 2 + rows * W * 2 + rows * top * 2 * EF * 2,
+              flops=rows * top * 2 * EF * W * 2, tensor=True)
+
+        def gating(k):
+            gu = torch.randn(rows * top, 2 * EF, device=dev).bfloat16()
+            y = torch.empty(rows * top, EF, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.gated_activation(gu, None, y, kernels.ACT_SILU)
+
+        timed(f"gated_activation (SiLU, experts' rows)/{label}", gating, rows * top * EF * 2 * 3)
+    return out
+
+
 def pekodra_kernels(size, pk):
     """Pekodra's own kernels alone at this size, timed like :func:`design_kernels`: 2,048 prompt rows of one sequence,
     and 64 decoded rows at context 2,048."""
@@ -1378,7 +1660,7 @@ def main():
     parser.add_argument("--workload", choices=["3b", "8b"], default=None,
                         help="run another workload instead of the headline one: continuous batching at the 3B sizes, "
                              "or a 2,048-token portion beside 64 decode rows at the 8B sizes")
-    parser.add_argument("--design", choices=["revesun", "pekodra", "kazodra"], default=None,
+    parser.add_argument("--design", choices=["revesun", "pekodra", "kazodra", "ladedra"], default=None,
                         help="instead of the headline workload: prefill and decode of this design beside a Llama of "
                              "equal layer sizes (--size), and the design's own kernels alone")
     args = parser.parse_args()

@@ -13,6 +13,10 @@
 // (both halves) in shared memory, and then take a quarter of the value columns each for the second product, over all
 // 64 keys.  The order of every sum follows from the row's position and the mask alone.  Prompt portions and decoded
 // rows take the same kernel: the rows of a portion read nearly the same keys and meet in L2.
+//
+// A step of few rows (decoded ones) gives every row several blocks, each over a run of the row's key tiles (how many
+// follows from the step's row count alone); they leave their running maximum, sum and unnormalised accumulator in
+// scratch memory, and a second small kernel adds the runs up in order.
 #include "common.cuh"
 
 namespace {
@@ -67,7 +71,7 @@ __global__ void __launch_bounds__(128)
 attention_latent_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ out, int64_t out_stride,
                         const bf16* __restrict__ cache, const int* __restrict__ positions,
                         const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride, int heads,
-                        int page_size, int mask_kind, int mask_size, float scale) {
+                        int page_size, int mask_kind, int mask_size, float scale, float* __restrict__ parts) {
     typedef Layout<D, DV> L;
     constexpr int KS = L::KS, PS = L::PS;
     constexpr int COLS = DV / 4;                                  // value columns a warp owns
@@ -79,6 +83,10 @@ attention_latent_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
     const int pos = positions[row], seq = seq_of_row[row];
     const int key_lo = (mask_kind == MASK_WINDOW && pos - mask_size + 1 > 0) ? pos - mask_size + 1 : 0;
     const int tiles = (pos - key_lo) / KT + 1;
+    // with `parts` the row's tiles are shared out among gridDim.z blocks, a run of neighbouring tiles each
+    const int per_split = (tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int tile_first = parts == nullptr ? 0 : min(tiles, (int)blockIdx.z * per_split);
+    const int tile_end = parts == nullptr ? tiles : min(tiles, tile_first + per_split);
     const int64_t page_elems = (int64_t)page_size * D;
     const int* table = block_table + (int64_t)seq * bt_stride;
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem);
@@ -106,7 +114,7 @@ attention_latent_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
         const bf16* src = q + (int64_t)row * q_stride + (int64_t)(there ? head0 + h : head0) * D + chunk * 8;
         cp_async16(base + L::Q_AT + h * KS + chunk * 16, src, there ? 16 : 0);
     }
-    fill(0);
+    if (tile_first < tile_end) fill(tile_first);
     cp_async_commit();
 
     float m[2] = {-1.0e30f, -1.0e30f}, l[2] = {0.0f, 0.0f};
@@ -116,8 +124,8 @@ attention_latent_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[j][e] = 0.0f;
 
-    for (int tile = 0; tile < tiles; ++tile) {
-        if (tile + 1 < tiles) {
+    for (int tile = tile_first; tile < tile_end; ++tile) {
+        if (tile + 1 < tile_end) {
             fill(tile + 1);
             cp_async_commit();
             cp_async_wait<1>();
@@ -220,6 +228,26 @@ attention_latent_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
         if (t == 0) stats[warp * 16 + g + r * 8] = l[r];
     }
     __syncthreads();
+    if (parts != nullptr) {                                       // this run's share: accumulator, maximum and sum
+        cp_async_wait<0>();                                       // (a block without tiles still waits for its queries' copy)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int head = head0 + g + r * 8;
+            if (head >= heads) continue;
+            float* mine = parts + (((int64_t)row * gridDim.z + blockIdx.z) * heads + head) * (DV + 2);
+#pragma unroll
+            for (int j = 0; j < COLS / 8; ++j)
+                *reinterpret_cast<float2*>(mine + warp * COLS + j * 8 + 2 * t) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+            if (warp == 0 && t == 0) {
+                float total = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) total += stats[w * 16 + g + r * 8];
+                mine[DV] = m[r];
+                mine[DV + 1] = total;
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int head = head0 + g + r * 8;
@@ -235,18 +263,57 @@ attention_latent_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
     }
 }
 
+// The runs of a row and head, added in order: out = sum_z o_z e^(m_z - M) / sum_z l_z e^(m_z - M), M the largest m_z.
+template <int DV>
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ parts, bf16* __restrict__ out, int64_t out_stride, int heads, int splits) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x, head = blockIdx.y;
+    const float* mine = parts + ((int64_t)row * splits * heads + head) * (DV + 2);
+    const int64_t step = (int64_t)heads * (DV + 2);
+    float top = -1.0e30f;
+    for (int z = 0; z < splits; ++z) top = fmaxf(top, mine[z * step + DV]);
+    float total = 0.0f;
+    for (int z = 0; z < splits; ++z) total = fmaf(mine[z * step + DV + 1], __expf(mine[z * step + DV] - top), total);
+    const float inv = 1.0f / fmaxf(total, 1.0e-30f);
+    for (int col = threadIdx.x; col < DV; col += 128) {
+        float value = 0.0f;
+        for (int z = 0; z < splits; ++z) value = fmaf(mine[z * step + col], __expf(mine[z * step + DV] - top), value);
+        out[(int64_t)row * out_stride + (int64_t)head * DV + col] = __float2bfloat16_rn(value * inv);
+    }
+}
+
+// Blocks a row in a step of `rows` rows: one where the rows alone fill the GPU, else as many runs of key tiles as bring
+// the grid to about two blocks a multiprocessor (at most 16).
+int splits_for(int rows, int heads) {
+    const int blocks = rows * ((heads + 15) / 16);
+    if (blocks >= 148) return 1;
+    const int splits = 296 / blocks;
+    return splits > 16 ? 16 : (splits < 1 ? 1 : splits);
+}
+
 template <int D, int DV>
 int launch(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache, const int* positions,
            const int* seq_of_row, const int* block_table, int bt_stride, int rows, int heads, int page_size, int mask_kind,
-           int mask_size, float scale, cudaStream_t stream) {
+           int mask_size, float scale, float* parts, cudaStream_t stream) {
     constexpr int smem = Layout<D, DV>::BYTES;
     auto kernel = attention_latent_kernel<D, DV>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return (int)err;
-    cudaError_t launched = tb_launch_pdl(kernel, dim3(rows, (heads + 15) / 16), dim3(128), (size_t)smem, stream,
+    const int splits = splits_for(rows, heads);
+    if (splits > 1 && parts == nullptr) return TB_ERR_BAD_SIZE;
+    cudaError_t launched = tb_launch_pdl(kernel, dim3(rows, (heads + 15) / 16, splits), dim3(128), (size_t)smem, stream,
                                          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, positions,
-                                         seq_of_row, block_table, bt_stride, heads, page_size, mask_kind, mask_size, scale);
-    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+                                         seq_of_row, block_table, bt_stride, heads, page_size, mask_kind, mask_size, scale,
+                                         splits > 1 ? parts : (float*)nullptr);
+    if (launched != cudaSuccess) return (int)launched;
+    if (splits > 1) {
+        launched = tb_launch_pdl(latent_merge_kernel<DV>, dim3(rows, heads), dim3(128), (size_t)0, stream, (const float*)parts,
+                                 (bf16*)out, out_stride, heads, splits);
+        if (launched != cudaSuccess) return (int)launched;
+    }
+    return tb_launch_status();
 }
 
 }  // namespace
@@ -256,12 +323,18 @@ TB_EXPORT int tb_attention_latent_mma_supported(int dim, int vdim) {
     return (dim == 576 && vdim == 512) || (dim == 288 && vdim == 256) || (dim == 160 && vdim == 128) ? 1 : 0;
 }
 
+// Blocks a row of a step of `rows` rows (1: no scratch is needed).
+TB_EXPORT int tb_attention_latent_mma_splits(int rows, int heads) {
+    return rows < 1 || heads < 1 ? 1 : splits_for(rows, heads);
+}
+
 // q: bfloat16 [rows, heads * dim] (row stride q_stride, elements); out: bfloat16 [rows, heads * vdim]; cache: this
-// layer's pages ([page_size][dim] a page); positions, seq_of_row: int32 [rows]; mask_kind: 0 causal, 1 window.
+// layer's pages ([page_size][dim] a page); positions, seq_of_row: int32 [rows]; mask_kind: 0 causal, 1 window; parts:
+// float32 [rows, splits, heads, vdim + 2] of scratch where tb_attention_latent_mma_splits says more than 1.
 TB_EXPORT int tb_attention_latent_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
                                       const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
                                       int rows, int heads, int dim, int vdim, int page_size, int mask_kind, int mask_size,
-                                      float scale, cudaStream_t stream) {
+                                      float scale, float* parts, cudaStream_t stream) {
     if (rows == 0) return 0;
     if (!tb_attention_latent_mma_supported(dim, vdim)) return TB_ERR_BAD_SIZE;
     if (heads < 1 || (heads + 15) / 16 > 65535 || page_size < 1) return TB_ERR_BAD_SIZE;
@@ -271,7 +344,7 @@ TB_EXPORT int tb_attention_latent_mma(const void* q, int64_t q_stride, void* out
         return TB_ERR_BAD_ALIGN;
 #define TB_ATTEND(D, DV)                                                                                             \
     return launch<D, DV>(q, q_stride, out, out_stride, cache, positions, seq_of_row, block_table, bt_stride, rows,   \
-                         heads, page_size, mask_kind, mask_size, scale, stream)
+                         heads, page_size, mask_kind, mask_size, scale, parts, stream)
     if (dim == 576) TB_ATTEND(576, 512);
     if (dim == 288) TB_ATTEND(288, 256);
     TB_ATTEND(160, 128);

@@ -29,14 +29,21 @@ typedef __nv_bfloat16 bf16;
 // 0 .. first_key(p) / pool - 1, then the tokens first_key(p) .. p.
 struct Extras {
     const float* sinks;
-    float softcap;
+    float softcap, cap_k;                 // cap_k = 2 log2(e) / softcap (0 without a cap)
     const bf16* pool_cache;
     const int* pool_table;
     int pool_bt_stride, pool;
 };
 
-__device__ __forceinline__ float capped(float s, float softcap) {
-    return softcap > 0.0f ? softcap * tanhf(s / softcap) : s;
+// softcap * tanh(s / softcap) as softcap - 2 softcap / (2^(s k) + 1) with k = 2 log2(e) / softcap: one exponential and
+// one reciprocal of the fast kind, good to some 1e-6 of softcap, which is far below what the bfloat16 queries and keys
+// of these kernels leave.  (2^(s k) = inf gives softcap, 0 gives -softcap.)
+__device__ __forceinline__ float capped(float s, float softcap, float k) {
+    if (softcap <= 0.0f) return s;
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(s * k));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return fmaf(-2.0f * softcap, r, softcap);
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
@@ -227,7 +234,7 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
                     const int r = e >> 1, place = j * 8 + 2 * t + (e & 1), key = key0 + place;
                     const bool seen = there[r] && (at0 + place < blocks_last ? at0 + place < blocks[r]
                                                                              : key <= pos[r] && key >= first_key[r]);
-                    s[j][e] = seen ? capped(s[j][e] * scale, x.softcap) : -1.0e30f;
+                    s[j][e] = seen ? capped(s[j][e] * scale, x.softcap, x.cap_k) : -1.0e30f;
                     top[r] = fmaxf(top[r], s[j][e]);
                 }
             float corr[2];
@@ -411,7 +418,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __rest
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int at = at0 + j * 8 + 2 * t + (e & 1);
-                    s[j][e] = at < span ? capped(s[j][e] * scale, x.softcap) : -1.0e30f;     // (all of the span is inside the mask)
+                    s[j][e] = at < span ? capped(s[j][e] * scale, x.softcap, x.cap_k) : -1.0e30f;     // (all of the span is inside the mask)
                     top[e >> 1] = fmaxf(top[e >> 1], s[j][e]);
                 }
             float corr[2];
@@ -554,7 +561,7 @@ TB_EXPORT int tb_attention_prompt_mma(const void* q, int64_t q_stride, void* out
         return TB_ERR_BAD_SIZE;
     if (softcap < 0.0f) return TB_ERR_BAD_SIZE;
     Extras x;
-    x.sinks = sinks; x.softcap = softcap; x.pool_cache = (const bf16*)pool_cache; x.pool_table = pool_table;
+    x.sinks = sinks; x.softcap = softcap; x.cap_k = softcap > 0.0f ? 2.8853900817779268f / softcap : 0.0f; x.pool_cache = (const bf16*)pool_cache; x.pool_table = pool_table;
     x.pool_bt_stride = pool_bt_stride; x.pool = pool;
     if (!tb_attention_prompt_mma_supported(dim, vdim)) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || page_size < 1 || num_seqs < 1) return TB_ERR_BAD_SIZE;
@@ -589,7 +596,7 @@ TB_EXPORT int tb_attention_rows_mma(const void* q, int64_t q_stride, void* out, 
         return TB_ERR_BAD_SIZE;
     if (softcap < 0.0f) return TB_ERR_BAD_SIZE;
     Extras x;
-    x.sinks = sinks; x.softcap = softcap; x.pool_cache = (const bf16*)pool_cache; x.pool_table = pool_table;
+    x.sinks = sinks; x.softcap = softcap; x.cap_k = softcap > 0.0f ? 2.8853900817779268f / softcap : 0.0f; x.pool_cache = (const bf16*)pool_cache; x.pool_table = pool_table;
     x.pool_bt_stride = pool_bt_stride; x.pool = pool;
     if (!tb_attention_prompt_mma_supported(dim, vdim)) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || heads / kv_heads > 16 || page_size < 1) return TB_ERR_BAD_SIZE;

@@ -3,7 +3,7 @@
 // and its attention kernel, in one pass over the projected rows.
 //
 // A projected row holds, side by side, H query heads of d numbers, G key heads of d numbers and G value heads of
-// dv numbers.  For queries and keys, of every head's first `rot_dims` numbers, number i and number i + rot_dims / 2
+// dv numbers; with `bias` (32-bit, as wide as that row) the projections' biases are added first, in 32-bit.  For queries and keys, of every head's first `rot_dims` numbers, number i and number i + rot_dims / 2
 // turn together by the angle position * inv_freq[i] (32-bit angle, sincosf), cosine and sine both multiplied by
 // `amplitude`; the rest of the head passes.  Then, with `unit_norm`, the head is divided by
 // sqrt(mean(head^2) + eps), the mean over all d numbers of the rotated head.  Queries go to q_out, keys and values
@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 rope_norm_cache_kernel(const T* __restrict__ proj, int64_t proj_stride, T* __restrict__ q_out, int64_t q_stride,
                        T* __restrict__ cache, const int* __restrict__ positions, const int* __restrict__ seq_of_row,
                        const int* __restrict__ block_table, int bt_stride, const float* __restrict__ inv_freq,
-                       HeadGeometry g, int write_kv) {
+                       const float* __restrict__ bias, HeadGeometry g, int write_kv) {
     extern __shared__ float head_cache[];             // kWarps * dim
     pdl_trigger();
     pdl_wait();                                       // the projected rows and the step's metadata come from kernels in front
@@ -59,14 +59,20 @@ rope_norm_cache_kernel(const T* __restrict__ proj, int64_t proj_stride, T* __res
             // a value head: copied as it is
             const int head = slot - g.heads - g.kv_heads;
             dst += (int64_t)g.kv_heads * g.page_size * g.dim + ((int64_t)head * g.page_size + in_page) * g.vdim;
-            const T* src = prow + (int64_t)(g.heads + g.kv_heads) * g.dim + (int64_t)head * g.vdim;
-            for (int i = lane; i < g.vdim; i += 32) dst[i] = src[i];
+            const int64_t at = (int64_t)(g.heads + g.kv_heads) * g.dim + (int64_t)head * g.vdim;
+            const T* src = prow + at;
+            if (bias == nullptr) {
+                for (int i = lane; i < g.vdim; i += 32) dst[i] = src[i];
+            } else {
+                for (int i = lane; i < g.vdim; i += 32) Elem<T>::store(dst + i, Elem<T>::load(src + i) + bias[at + i]);
+            }
             return;
         }
     } else {
         dst = q_out + (int64_t)row * q_stride + (int64_t)slot * g.dim;
     }
     const T* src = prow + (int64_t)slot * g.dim;      // query heads and key heads lie side by side in the row
+    const float* add = bias == nullptr ? nullptr : bias + (int64_t)slot * g.dim;
     float* mine = head_cache + warp * g.dim;
     const int half = g.rot_dims >> 1;
     float ss = 0.0f;
@@ -75,7 +81,11 @@ rope_norm_cache_kernel(const T* __restrict__ proj, int64_t proj_stride, T* __res
         sincosf((float)pos * inv_freq[i], &sn, &cs);
         sn *= g.amplitude;
         cs *= g.amplitude;
-        const float u = Elem<T>::load(src + i), v = Elem<T>::load(src + i + half);
+        float u = Elem<T>::load(src + i), v = Elem<T>::load(src + i + half);
+        if (add != nullptr) {
+            u += add[i];
+            v += add[i + half];
+        }
         const float r0 = u * cs - v * sn;
         const float r1 = v * cs + u * sn;
         mine[i] = r0;
@@ -84,7 +94,7 @@ rope_norm_cache_kernel(const T* __restrict__ proj, int64_t proj_stride, T* __res
         ss = fmaf(r1, r1, ss);
     }
     for (int i = g.rot_dims + lane; i < g.dim; i += 32) {
-        const float v = Elem<T>::load(src + i);
+        const float v = Elem<T>::load(src + i) + (add != nullptr ? add[i] : 0.0f);
         mine[i] = v;
         ss = fmaf(v, v, ss);
     }
@@ -132,10 +142,11 @@ pool_blocks_kernel(const T* __restrict__ cache, T* __restrict__ pool_cache, cons
 }  // namespace
 
 // proj: [rows, >= (H + G) * d + G * dv] with row stride proj_stride (elements); q_out: [rows, H * d] with row
-// stride q_stride; cache: this layer's pages; inv_freq: 32-bit [rot_dims / 2] (may be null when rot_dims is 0).
+// stride q_stride; cache: this layer's pages; inv_freq: 32-bit [rot_dims / 2] (may be null when rot_dims is 0); bias:
+// null or 32-bit [(H + G) * d + G * dv].
 TB_EXPORT int tb_rope_norm_cache(const void* proj, int64_t proj_stride, void* q_out, int64_t q_stride, void* cache,
                                  const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
-                                 const float* inv_freq, float amplitude, int rows, int heads, int kv_heads, int dim,
+                                 const float* inv_freq, const float* bias, float amplitude, int rows, int heads, int kv_heads, int dim,
                                  int vdim, int rot_dims, int unit_norm, float eps, int page_size, int write_kv,
                                  int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
@@ -154,11 +165,11 @@ TB_EXPORT int tb_rope_norm_cache(const void* proj, int64_t proj_stride, void* q_
     if (dtype == TB_F32)
         launched = tb_launch_pdl(rope_norm_cache_kernel<float>, grid, dim3(kWarps * 32), smem, stream, (const float*)proj,
                                  proj_stride, (float*)q_out, q_stride, (float*)cache, positions, seq_of_row, block_table,
-                                 bt_stride, inv_freq, g, write_kv);
+                                 bt_stride, inv_freq, bias, g, write_kv);
     else if (dtype == TB_BF16)
         launched = tb_launch_pdl(rope_norm_cache_kernel<__nv_bfloat16>, grid, dim3(kWarps * 32), smem, stream,
                                  (const __nv_bfloat16*)proj, proj_stride, (__nv_bfloat16*)q_out, q_stride,
-                                 (__nv_bfloat16*)cache, positions, seq_of_row, block_table, bt_stride, inv_freq, g,
+                                 (__nv_bfloat16*)cache, positions, seq_of_row, block_table, bt_stride, inv_freq, bias, g,
                                  write_kv);
     else
         return TB_ERR_BAD_DTYPE;

@@ -1106,8 +1106,9 @@ def embedding_scaled(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tenso
 def rope_norm_cache(proj: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
                     seq_of_row: torch.Tensor, block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], *,
                     amplitude: float, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int,
-                    unit_norm: bool, eps: float, page_size: int, write_kv: bool = True) -> None:
-    """Rotate-half rotation of the first ``rot_dims`` numbers of every query and key head of ``proj`` (cosine and sine
+                    unit_norm: bool, eps: float, page_size: int, write_kv: bool = True,
+                    bias: Optional[torch.Tensor] = None) -> None:
+    """With ``bias`` (float32, as wide as the projected row) the projections' biases are added first.  Rotate-half rotation of the first ``rot_dims`` numbers of every query and key head of ``proj`` (cosine and sine
     times ``amplitude``), then, with ``unit_norm``, every head over ``sqrt(mean(head^2) + eps)``; queries into ``q_out``,
     keys and values into the pages of ``cache`` (``[kv_heads, page, dim]`` keys then ``[kv_heads, page, vdim]`` values)."""
     _cuda(proj, q_out, cache, positions, seq_of_row, block_table, inv_freq)
@@ -1121,10 +1122,13 @@ def rope_norm_cache(proj: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor
               and inv_freq.is_contiguous(), "rope_norm_cache inv_freq")
     for t in (positions, seq_of_row, block_table):
         _need(t.dtype == torch.int32, "rope_norm_cache metadata must be int32")
+    if bias is not None:
+        _cuda(bias)
+        _need(bias.dtype == torch.float32 and bias.numel() == channels and bias.is_contiguous(), "rope_norm_cache bias")
     lib = load_library("rope_norm_cache")
     _check(lib.tb_rope_norm_cache(_ptr(proj), _i64(proj.stride(0)), _ptr(q_out), _i64(q_out.stride(0)), _ptr(cache),
                                   _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
-                                  _ptr(inv_freq), _f32(amplitude), _i32(rows), _i32(heads), _i32(kv_heads), _i32(dim),
+                                  _ptr(inv_freq), _ptr(bias), _f32(amplitude), _i32(rows), _i32(heads), _i32(kv_heads), _i32(dim),
                                   _i32(vdim), _i32(rot_dims), _i32(1 if unit_norm else 0), _f32(eps), _i32(page_size),
                                   _i32(1 if write_kv else 0), _i32(_code(proj.dtype)), _stream()), "rope_norm_cache")
 
@@ -1472,7 +1476,8 @@ def attention_latent_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
                          page_size: int, mask_kind: int, mask_size: int, scale: float) -> torch.Tensor:
     """:func:`attention_masked` with ``kv_heads = 1`` and ``keys_per_value = 0`` (pages of ``[page_size, dim]`` vectors
     whose first ``vdim`` numbers are the value) on the tensor cores, for bfloat16: a block a row and sixteen query heads;
-    exact bfloat16 products with 32-bit accumulation for the scores, 32-bit softmax, the weights as two bfloat16 halves."""
+    exact bfloat16 products with 32-bit accumulation for the scores, 32-bit softmax, the weights as two bfloat16 halves.
+    In a step of few rows every row's keys are shared out among several blocks, and a second kernel adds their results."""
     _cuda(q, out, cache, positions, seq_of_row, block_table)
     rows = q.shape[0]
     _need(q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_latent_mma q")
@@ -1480,8 +1485,14 @@ def attention_latent_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
     _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_latent_mma cache")
     _need(mask_kind in (MASK_CAUSAL, MASK_WINDOW), "attention_latent_mma mask")
     lib = load_library("attention_latent_mma")
+    # a step of few rows gives every row several blocks, each over a run of its keys; they meet through this scratch
+    splits = lib.tb_attention_latent_mma_splits(_i32(rows), _i32(heads))
+    parts = torch.empty((rows, splits, heads, vdim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     _check(lib.tb_attention_latent_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                        _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
                                        _i32(rows), _i32(heads), _i32(dim), _i32(vdim), _i32(page_size), _i32(mask_kind),
-                                       _i32(mask_size), _f32(scale), _stream()), "attention_latent_mma")
+                                       _i32(mask_size), _f32(scale), _ptr(parts), _stream()), "attention_latent_mma")
+    if splits > 1:
+        global launch_count
+        launch_count += 1          # (the kernel that adds the runs up)
     return out

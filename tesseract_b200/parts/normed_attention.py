@@ -82,8 +82,12 @@ class NormedAttention(Mixer):
             raise ValueError("the attention kernel takes keys of up to 1024 and values of up to 512 numbers a head")
         self.q_width = self.num_heads * self.key_dim
         self.o_width = self.num_heads * self.value_dim
-        bias = torch.cat([tensors["q_bias"], tensors["k_bias"], tensors["v_bias"]]) if self.biased else None
-        self.in_proj = Linear(torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0), runtime, bias=bias)
+        # (the biases are added by the kernel behind the product, in 32-bit, in front of its rotation)
+        self.in_bias = None
+        if self.biased:
+            self.in_bias = torch.cat([tensors["q_bias"], tensors["k_bias"], tensors["v_bias"]]).to(
+                device=runtime.device, dtype=torch.float32).contiguous()
+        self.in_proj = Linear(torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0), runtime)
         self.o_proj = Linear(tensors["o"], runtime)
         position_spec = spec.children.get("position") or PartSpec.make("none")
         self.position = POSITION_ENCODINGS.get(position_spec.kind)(position_spec, {}, runtime)
@@ -161,7 +165,8 @@ class NormedAttention(Mixer):
         kernels.rope_norm_cache(proj, q, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table, self.inv_freq,
                                 amplitude=self.amplitude, heads=self.num_heads, kv_heads=self.num_kv_heads,
                                 dim=self.key_dim, vdim=self.value_dim, rot_dims=self.rot_dims,
-                                unit_norm=self.unit_norm, eps=self.qk_norm_eps, page_size=cache.page_size)
+                                unit_norm=self.unit_norm, eps=self.qk_norm_eps, page_size=cache.page_size,
+                                bias=self.in_bias)
         extras = {"sinks": self.sinks, "softcap": self.softcap}
         if pooled is not None:
             pool_table = ctx.groups[pooled.group].block_table
