@@ -5,7 +5,7 @@
 //            positions of a sequence are cut into consecutive blocks of `mask_size`, counted from position 0, and
 //            a row sees the keys of its own block up to its own position), or a window with pooled blocks: beside
 //            the window's keys a row at position p sees one averaged key and value for every block of `pool`
-//            positions that lies wholly in front of the window (block b if b * pool + pool - 1 <= p - mask_size);
+//            positions that ends in front of the window (block b if (b + 1) * pool <= p - mask_size + 1);
 //            the averages live in pages of their own (entry b of the request's pooled pages, same page layout), are
 //            walked first, and share the softmax with the window's keys;
 //   sink     the softmax denominator has one more entry that carries no value, of score 0

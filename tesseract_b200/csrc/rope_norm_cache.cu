@@ -130,10 +130,17 @@ pool_blocks_kernel(const T* __restrict__ cache, T* __restrict__ pool_cache, cons
         const int width = is_key ? dim : vdim, c = is_key ? col : col - dim;
         const int64_t part = is_key ? 0 : (int64_t)kv_heads * page_size * dim;
         float sum = 0.0f;
-        for (int j = 0; j < pool; ++j) {
-            const int key = first + j;
-            const int64_t page = (int64_t)table[key / page_size] * page_elems;
-            sum += Elem<T>::load(cache + page + part + ((int64_t)g * page_size + key % page_size) * width + c);
+        for (int j0 = 0; j0 < pool; j0 += 8) {         // eight loads in flight, then their sum in position order
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int key = first + min(j0 + u, pool - 1);
+                const int64_t page = (int64_t)table[key / page_size] * page_elems;
+                v[u] = Elem<T>::load(cache + page + part + ((int64_t)g * page_size + key % page_size) * width + c);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (j0 + u < pool) sum += v[u];
         }
         Elem<T>::store(pool_cache + to_page + part + ((int64_t)g * page_size + to_in_page) * width + c, sum / (float)pool);
     }

@@ -820,7 +820,7 @@ def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     ``[kv_heads / keys_per_value, page_size, vdim]`` values, key head ``g`` reading value head ``g // keys_per_value``;
     ``keys_per_value = 0``: pages hold keys only and a key's first ``vdim`` numbers are its value.  ``mask_kind``:
     causal, window or blocks of ``mask_size`` positions, or ``MASK_WINDOW_POOLED``: a window and, in front of it, one
-    averaged key and value per block of ``pool`` positions that lies wholly before the window, from
+    averaged key and value per block of ``pool`` positions that ends in front of the window, from
     ``pooled = (pages of the averages, their block table, pool)``; ``sink``: one more entry of score 0 in the softmax's
     denominator, or, with ``sinks`` (float32 ``[heads]``), of a learned score per head; ``softcap`` > 0: a score ``s``
     becomes ``softcap * tanh(s / softcap)``."""

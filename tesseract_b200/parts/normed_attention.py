@@ -9,10 +9,10 @@ Per row ``h`` (the mixer's input):
   (no weight); rotated, normalised keys and the values go into the request's pages;
 * every row attends over the keys its mask lets it see: ``causal`` (all up to its own position), ``window`` (its own
   and the ``size - 1`` positions before it; older pages go back to the pool) or ``window_pooled``: the window and, for
-  every block of ``pool`` positions that lies wholly in front of it (block ``b`` holds ``b * pool .. b * pool + pool - 1``
-  and is seen from position ``p`` if ``b * pool + pool - 1 <= p - size``), one key and one value that are the averages of
-  the block's keys and values as the pages hold them; tokens that have left the window and whose block is not yet seen
-  are not seen.  The averages live in pages of their own (an entry a block) and are written by the step that brings a
+  every block of ``pool`` positions that ends in front of it (blocks are counted from position 0; block ``b`` is seen
+  from position ``p`` if ``(b + 1) * pool <= p - size + 1``), one key and one value that are the averages of the block's
+  keys and values as the pages hold them; so for up to ``pool - 1`` steps a token is visible neither by itself nor through
+  its block.  The averages live in pages of their own (an entry a block) and are written by the step that brings a
   block's last token.  Scores ``(q . k) * scale``, with ``softcap`` then ``softcap * tanh(score / softcap)``, the softmax
   and the weights are 32-bit; with ``sink`` the denominator also holds ``exp`` of a learned number per query head;
 * with ``bias`` the three projections add a bias each;

@@ -136,7 +136,7 @@ def latent_attention(m, w, h, eps, store=identity):
 
 def pooled_window_attention(m, w, h, eps, store=identity):
     """Grouped-query attention over the last ``mask.size`` tokens and one averaged key and value per block of
-    ``mask.pool`` tokens that lies wholly in front of them; a learned number per head joins the denominator."""
+    ``mask.pool`` tokens that ends in front of them; a learned number per head joins the denominator."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     size, P, cap = m["mask"]["size"], m["mask"]["pool"], m.get("softcap")
@@ -154,7 +154,7 @@ def pooled_window_attention(m, w, h, eps, store=identity):
     out = np.zeros((T, H, dv))
     for t in range(T):
         first = max(0, t - size + 1)
-        seen = [b for b in range(blocks) if b * P + P - 1 <= t - size]
+        seen = [b for b in range(blocks) if (b + 1) * P <= t - size + 1]
         for head in range(H):
             g = head // (H // G)
             keys = np.concatenate([pooled_k[seen, g], k[first:t + 1, g]])
