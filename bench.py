@@ -795,7 +795,7 @@ def ladedra_config(size, layers):
                                     "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, heads - 1)) for h in range(heads)],
                                     "rot": {"dims": p["ret_dim"], "base": 10000.0}},
                           "left_scale": 1.0, "right_scale": 1.0},
-                "mlp": {"kind": "moe", "router": {"experts": p["experts"], "top": p["top"], "scale": 2.5,
+                "mlp": {"kind": "moe", "router": {"experts": p["experts"], "top": p["top"], "scale": 2.0,
                                                   "groups": {"count": p["groups"][0], "keep": p["groups"][1]}},
                         "expert": {"ff": p["expert_ff"]}, "shared": {"ff": p["shared_ff"]}}}
     return {"architecture": "Ladedra", "torch_dtype": "bfloat16", "width": z["width"], "vocab": DESIGN_VOCAB,
@@ -1386,7 +1386,7 @@ def ladedra_kernels(size, pk):
 
         def blend(k):
             a, b = torch.randn(rows, W, device=dev), torch.randn(rows, W, device=dev)
-            return lambda: kernels.blend_rows(a, b, 1.2, 0.9)
+            return lambda: kernels.blend_rows(a, b, 1.5, 0.5)
 
         timed(f"blend_rows/{label}", blend, rows * W * 4 * 3)
 
@@ -1429,7 +1429,7 @@ def ladedra_kernels(size, pk):
             ids = torch.empty(rows, top, dtype=torch.int32, device=dev)
             weights = torch.empty(rows, top, dtype=torch.float32, device=dev)
             return lambda: kernels.choose_grouped(router.forward(x, float32_out=True), ids, weights, groups=groups, keep=keep,
-                                                  weight_scale=2.5)
+                                                  weight_scale=2.0)
 
         timed(f"router (product with 32-bit logits, choice among groups)/{label}", route, rows * W * 2 + E * W * 2,
               flops=rows * E * W * 2)

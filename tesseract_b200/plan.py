@@ -320,6 +320,10 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                     lines.append(f"      {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
                 if hasattr(mixer, "attention_choice"):
                     lines.append(f"      attend     {mixer.attention_choice(rows)}")
+                elif hasattr(mixer, "sides"):              # mixers side by side: each one's attention kernel
+                    for side in mixer.sides:
+                        if hasattr(side, "attention_choice"):
+                            lines.append(f"      attend     '{side.kind}': {side.attention_choice(rows)}")
                 elif hasattr(mixer, "num_kv_heads") and hasattr(mixer, "value_dim") and not hasattr(mixer, "taps"):
                     per = mixer.num_heads // mixer.num_kv_heads
                     lines.append(f"      attend     {masked_attention(dtype, rows, mixer.key_dim, mixer.value_dim, heads_per_kv=per)}")
@@ -337,6 +341,11 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                     lines.append(f"      {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
             elif ffn is not None:
                 lines.append(f"    feed-forward '{ffn.kind}' (its own code)")
+            gates = getattr(block, "gates", None)
+            if gates is not None and hasattr(gates, "products"):
+                lines.append(f"    residual gates '{gates.kind}' (the weighting, the addition and the next norm are one kernel)")
+                for name, linear, epilogue in gates.products():
+                    lines.append(f"      {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
     for index, injection in enumerate(getattr(model, "injections", ())):
         entries = [i for i, entry in enumerate(model.spec.run_order) if entry.inject == index]
         lines.append(f"injection '{injection.kind}' in front of run entries {entries}")

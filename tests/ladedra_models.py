@@ -75,7 +75,7 @@ TINY_LADEDRA = {
                            moe(5, 1, 24, None, None, 1.0)),
                      layer(parallel(window_attention(6, 3, 8, 12, 40, 7, None, 0.7, 50.0),
                                     retention(2, 8, 16, (0.0, 1.0), rot(4, 10.0)), 1.1, 0.9), None),
-                     layer(latent(4, 8, 6, 4, 8, rot(6, 20.0, (16.0, 8, 4.0, 0.5)), 0.3), moe(8, 3, 8, 16, (4, 2), 2.5))]},
+                     layer(latent(4, 8, 6, 4, 8, rot(6, 20.0, (16.0, 8, 4.0, 0.5)), 0.3), moe(8, 3, 8, 16, (4, 2), 1.25))]},
     # widths that are no multiple of four or eight; a pool of one token and a window of one; every expert its own group
     "c": {"architecture": "Ladedra", "width": 42, "vocab": 77, "norm": {"eps": 1e-4}, "embedding": {"scale": 6.5},
           "layers": [layer(latent(1, 10, 6, 14, 9, rot(6, 30.0, (2.0, 16, 2.0, 1.0)), 0.3), moe(4, 2, 10, 6, (4, 3), 0.5)),
@@ -85,7 +85,7 @@ TINY_LADEDRA = {
                                     retention(3, 6, 5, (1.0, 0.5, 0.99), rot(6, 50.0)), 0.8, 1.2), None)]},
     # a window longer than any prompt of the tests (no block is ever seen); a latent without a rotated part
     "d": {"architecture": "Ladedra", "width": 32, "vocab": 64, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5},
-          "layers": [layer(parallel(window_attention(4, 1, 8, 8, 1000, 16, rot(8, 20.0), 0.35, 20.0),
+          "layers": [layer(parallel(window_attention(4, 1, 8, 8, 1000, 16, rot(8, 20.0), 0.35, 12.0),
                                     retention(2, 8, 8, (0.95, 0.5), rot(8, 20.0)), 1.0, 0.5), dense(16)),
                      layer(latent(4, 8, 0, 4, 8, None, 0.3), dense(24)),
                      layer(parallel(window_attention(2, 1, 24, 8, 16, 16, rot(12, 9.0), 0.2, 10.0),
@@ -94,8 +94,8 @@ TINY_LADEDRA = {
     "e": {"architecture": "Ladedra", "width": 64, "vocab": 90, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
           "layers": [layer(latent(2, 64, 32, 128, 128, rot(32, 10000.0, (8.0, 128, 16.0, 1.0)), 0.1), dense(48)),
                      layer(parallel(window_attention(4, 1, 64, 64, 100, 32, rot(64, 10000.0), 0.125, 30.0),
-                                    retention(2, 64, 64, (0.95, 0.99), rot(32, 1000.0)), 1.2, 0.9),
-                           moe(8, 2, 32, 40, (2, 1), 2.0)),
+                                    retention(2, 64, 64, (0.95, 0.99), rot(32, 1000.0)), 1.4, 0.8),
+                           moe(8, 3, 32, 40, (4, 2), 2.0)),
                      layer(parallel(window_attention(2, 2, 128, 64, 64, 8, rot(64, 100.0), 0.09, 25.0),
                                     retention(2, 32, 128, (0.9, 1.0), None), 0.7, 1.4), None)]},
 }
@@ -134,12 +134,12 @@ def random_config(seed: int) -> dict:
             dim = r.choice([6, 8, 12, 16, 24, 32, 64, 128])
             left = window_attention(heads, kv_heads, dim, r.choice([4, 8, 10, 16, 24, 48, 64, 128]),
                                     r.choice([1, 3, 16, 17, 50, 64, 120, 500]), r.choice([1, 2, 5, 8, 16, 33, 40]),
-                                    rotation(dim), r.choice([0.9 * dim ** -0.5, 0.3, 0.07]), r.choice([5.0, 20.0, 50.0]))
+                                    rotation(dim), r.choice([0.9 * dim ** -0.5, 0.3, 0.07]), r.choice([5.0, 15.0, 50.0]))
             rheads = r.choice([1, 2, 3, 4, 6])
             rdim = r.choice([4, 8, 16, 24, 32, 64])
             right = retention(rheads, rdim, r.choice([4, 10, 16, 33, 48, 64, 80]),
                               [r.choice([0.0, 0.3, 0.9, 0.99, 0.9999, 1.0]) for _ in range(rheads)], rotation(rdim))
-            mixer = parallel(left, right, r.choice([1.0, 1.2, 0.4]), r.choice([1.0, 0.9, 1.6]))
+            mixer = parallel(left, right, r.choice([1.0, 1.3, 0.4]), r.choice([1.0, 0.8, 1.6]))
         kind = r.choice(["none", "dense", "moe", "moe"])
         if kind == "none":
             mlp = None
@@ -150,7 +150,7 @@ def random_config(seed: int) -> dict:
             per = r.choice([1, 2, 4])
             keep = r.randint(1, groups)
             mlp = moe(groups * per, r.randint(1, min(4, keep * per)), r.choice([8, 16, 40, 64]), r.choice([None, 8, 48]),
-                      r.choice([None, (groups, keep)]) if (groups, keep) == (1, 1) else (groups, keep), r.choice([1.0, 2.5, 0.7]))
+                      r.choice([None, (groups, keep)]) if (groups, keep) == (1, 1) else (groups, keep), r.choice([1.0, 1.75, 0.7]))
         layers.append(layer(mixer, mlp))
     return {"architecture": "Ladedra", "width": width, "vocab": r.randint(40, 700), "norm": {"eps": r.choice([1e-5, 1e-6])},
             "embedding": {"scale": r.choice([1.0, 4.0, 12.0])}, "layers": layers}

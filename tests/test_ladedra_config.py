@@ -123,7 +123,7 @@ def test_random_configurations_describe_and_write(tmp_path, seed):
     assert set(tensors) == set(expected_tensors(spec))
 
 
-@pytest.mark.parametrize("dims,base,scaling", [(8, 1000.0, (4.0, 32, 8.0, 1.0)), (32, 20000.0, (8.0, 2048, 32.0, 1.0)),
+@pytest.mark.parametrize("dims,base,scaling", [(8, 1000.0, (4.0, 32, 8.0, 1.0)), (32, 30000.0, (6.0, 1024, 16.0, 1.0)),
                                                (6, 30.0, (2.0, 16, 2.0, 1.0)), (64, 1e6, (40.0, 4096, 32.0, 0.5)), (4, 50.0, None)])
 def test_stretched_frequencies_agree_with_the_plain_recipe(dims, base, scaling):
     named = dict(zip(("factor", "original", "fast", "slow"), scaling)) if scaling else None
