@@ -136,15 +136,15 @@ def test_squared_relu_feed_forward(dtype, width, ff):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width,experts,top,ff,shared,groups,scale", [(48, 6, 2, 16, 24, (3, 2), 1.5), (64, 5, 1, 24, None, None, 1.0),
                                                                     (42, 4, 2, 10, 6, (4, 3), 0.5), (128, 16, 4, 64, 96, (4, 2), 2.0)])
-@pytest.mark.parametrize("rows", [1, 9, 300])
+@pytest.mark.parametrize("rows", [2, 9, 300])
 def test_gated_experts_routed_within_groups(dtype, width, experts, top, ff, shared, groups, scale, rows):
-    """The routed feed-forward alone: rows whose router decides by a wide margin (its logits are spread out), so that the
-    same experts are chosen in both precisions, against the plain function row by row."""
+    """The routed feed-forward alone against the plain function, row by row, at the rows whose router does not decide by
+    so little that a rounding could turn the choice."""
     from tesseract_b200.config.spec import PartSpec
     from tesseract_b200.parts import FEED_FORWARDS
 
     g = torch.Generator().manual_seed(width + experts + rows)
-    named = {"router": torch.randn(experts, width, generator=g) * (6.0 * width ** -0.5)}
+    named = {"router": torch.randn(experts, width, generator=g) * (1.5 * width ** -0.5)}
     weights = {"router": "router"}
     for e in range(experts):
         named.update({f"e{e}.gate": torch.randn(ff, width, generator=g) * width ** -0.5, f"e{e}.up": torch.randn(ff, width, generator=g) * width ** -0.5,
@@ -170,8 +170,8 @@ def test_gated_experts_routed_within_groups(dtype, width, experts, top, ff, shar
     gaps = {}
     want = plain.expert_feed_forward(mlp, as_plain(named), h.double().numpy(), close_calls=gaps)
     coarse = plain.expert_feed_forward(mlp, as_plain(named), h.double().numpy(), plain.bfloat16)
-    steady = [t for t in range(rows) if gaps.get(t, 1.0) >= 0.02]
-    assert len(steady) >= rows * 0.7
+    steady = [t for t in range(rows) if gaps.get(t, 1.0) >= 0.01]
+    assert len(steady) >= max(1, rows // 3)
     noise = float(np.abs(coarse - want)[steady].max()) if dtype == torch.bfloat16 else 0.0
     got = part.forward(h.to(dtype).to(dev()), step_context(range(rows), [None], 16))
     assert got.dtype == torch.float32 and torch.isfinite(got).all()
