@@ -125,6 +125,26 @@ __global__ void sigmoid_mul_kernel(const T* __restrict__ a, int64_t a_stride, co
         Elem<T>::store(o + j, Elem<T>::load(ar + j) * (1.0f / (1.0f + expf(-Elem<T>::load(gr + j)))));
 }
 
+// 16-byte packets of a, g and out (width a multiple of the packet, rows aligned).
+template <typename T>
+__global__ void sigmoid_mul_packets_kernel(const T* __restrict__ a, int64_t a_stride, const T* __restrict__ g, int64_t g_stride,
+                                           T* __restrict__ out, int64_t out_stride, int width) {
+    constexpr int N = Packet<T>::N;
+    pdl_trigger();
+    pdl_wait();
+    const T* ar = a + (int64_t)blockIdx.x * a_stride;
+    const T* gr = g + (int64_t)blockIdx.x * g_stride;
+    T* o = out + (int64_t)blockIdx.x * out_stride;
+    for (int j = (blockIdx.y * blockDim.x + threadIdx.x) * N; j < width; j += gridDim.y * blockDim.x * N) {
+        float av[N], gv[N];
+        Packet<T>::load(ar + j, av);
+        Packet<T>::load(gr + j, gv);
+#pragma unroll
+        for (int e = 0; e < N; ++e) av[e] *= 1.0f / (1.0f + expf(-gv[e]));
+        Packet<T>::store(o + j, av);
+    }
+}
+
 template <typename T>
 __global__ void embedding_scaled_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab, float s) {
@@ -241,6 +261,20 @@ TB_EXPORT int tb_add_rows(float* a, const float* b, int64_t total, cudaStream_t 
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
+template <typename T>
+static cudaError_t launch_sigmoid_mul(const void* a, int64_t a_stride, const void* g, int64_t g_stride, void* out, int64_t out_stride,
+                               int rows, int width, cudaStream_t stream) {
+    constexpr int N = Packet<T>::N;
+    const int threads = 256;
+    const bool packets = width % N == 0 && a_stride % N == 0 && g_stride % N == 0 && out_stride % N == 0 &&
+                         ((uintptr_t)a | (uintptr_t)g | (uintptr_t)out) % 16 == 0;
+    if (packets)
+        return tb_launch_pdl(sigmoid_mul_packets_kernel<T>, row_grid(rows, width, threads, N), dim3(threads), 0, stream,
+                             (const T*)a, a_stride, (const T*)g, g_stride, (T*)out, out_stride, width);
+    return tb_launch_pdl(sigmoid_mul_kernel<T>, row_grid(rows, width, threads), dim3(threads), 0, stream, (const T*)a,
+                         a_stride, (const T*)g, g_stride, (T*)out, out_stride, width);
+}
+
 TB_EXPORT int tb_blend_rows(float* a, const float* b, int64_t total, float x, float y, cudaStream_t stream) {
     if (total == 0) return 0;
     cudaError_t launched = tb_launch_pdl(blend_rows_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, a, b, total, x, y);
@@ -250,15 +284,11 @@ TB_EXPORT int tb_blend_rows(float* a, const float* b, int64_t total, float x, fl
 TB_EXPORT int tb_sigmoid_mul(const void* a, int64_t a_stride, const void* g, int64_t g_stride, void* out, int64_t out_stride,
                              int rows, int width, int dtype, cudaStream_t stream) {
     if (rows == 0 || width == 0) return 0;
-    const int threads = 256;
     cudaError_t launched;
     if (dtype == TB_F32)
-        launched = tb_launch_pdl(sigmoid_mul_kernel<float>, row_grid(rows, width, threads), dim3(threads), 0, stream,
-                                 (const float*)a, a_stride, (const float*)g, g_stride, (float*)out, out_stride, width);
+        launched = launch_sigmoid_mul<float>(a, a_stride, g, g_stride, out, out_stride, rows, width, stream);
     else if (dtype == TB_BF16)
-        launched = tb_launch_pdl(sigmoid_mul_kernel<__nv_bfloat16>, row_grid(rows, width, threads), dim3(threads), 0, stream,
-                                 (const __nv_bfloat16*)a, a_stride, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out,
-                                 out_stride, width);
+        launched = launch_sigmoid_mul<__nv_bfloat16>(a, a_stride, g, g_stride, out, out_stride, rows, width, stream);
     else
         return TB_ERR_BAD_DTYPE;
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
